@@ -8,6 +8,8 @@
 // (causal and same-chunk mask of llama4/llama4_jax/model.py:731-742; scale dh^-0.5, model.py:774;
 // 32-bit softmax, model.py:789).  Queries of layers with temperature tuning are scaled by
 // 1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)).
+// With `sink` (one number per query head) the softmax has one more term in its denominator, exp(sink[h]), which
+// carries no value: weights p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); a sink of 0 adds one to the denominator.
 // The order of the key loop depends only on (start, p): a position's result does not change with
 // what else is in the batch or how the prompt was cut into steps.
 #include "common.cuh"
@@ -22,7 +24,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                          T* __restrict__ out, int Hq, int Hkv, int dh, int page_size, int num_pages,
                                          float scale, int chunk, int window, float attn_scale, float floor_scale,
-                                         int* status) {
+                                         const float* __restrict__ sink, int* status) {
   JLX_TL(TL_ATTN_GENERIC);
   extern __shared__ float smem[];
   const int n = blockIdx.x, hk = blockIdx.y;
@@ -102,10 +104,16 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
       }
     }
     if (active) {
+      float corr = 1.f;
+      if (sink) {  // the sink joins the sum like a last key without a value
+        const float m_new = fmaxf(m, sink[h]);
+        corr = expf(m - m_new);
+        l = l * corr + expf(sink[h] - m_new);
+      }
 #pragma unroll
       for (int i = 0; i < ATT_MAX_D32; ++i) {
         const int d = lane + 32 * i;
-        if (i < nd && d < dh) out[((size_t)n * Hq + h) * dh + d] = from_f32<T>(acc[i] / l);
+        if (i < nd && d < dh) out[((size_t)n * Hq + h) * dh + d] = from_f32<T>(acc[i] * corr / l);
       }
     }
     __syncthreads();
@@ -115,7 +123,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 JLX_API int jlx_attention_generic(const void* q, const void* pages, int dtype, const int* block_table, int bt_stride,
                                   const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv,
                                   int dh, int page_size, int num_pages, float scale, int chunk, int window,
-                                  float attn_scale, float floor_scale, int* status, cudaStream_t stream) {
+                                  float attn_scale, float floor_scale, const float* sink, int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && dh > 0 && page_size > 0 && num_pages > 0, "attention: bad sizes");
   JLX_REQUIRE(Hq % Hkv == 0, "attention: %d query heads are no multiple of %d KV heads", Hq, Hkv);
   JLX_REQUIRE(dh <= 32 * ATT_MAX_D32, "attention: head size %d is above the supported maximum %d", dh, 32 * ATT_MAX_D32);
@@ -130,7 +138,7 @@ JLX_API int jlx_attention_generic(const void* q, const void* pages, int dtype, c
       JLX_CUDA(cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attention_generic_kernel<T><<<dim3(N, Hkv), nwarp * 32, smem, stream>>>(
         (const T*)q, (const T*)pages, block_table, bt_stride, req_of_token, positions, (T*)out, Hq, Hkv, dh, page_size,
-        num_pages, scale, chunk, window, attn_scale, floor_scale, status);
+        num_pages, scale, chunk, window, attn_scale, floor_scale, sink, status);
   });
   JLX_LAUNCH_CHECK("attention_generic");
   return 0;

@@ -86,6 +86,7 @@ struct AttnParams {
   int max_splits;
   const int* rows;      // optional, decode: the token rows to work on (null: rows 0..N-1); partials are indexed by the list's order
   int split_keys;       // keys per decode split (a multiple of SPLIT_UNIT)
+  const float* sink;    // optional, [Hq]: one more term exp(sink[h]) in the softmax's denominator, without a value
 };
 
 __device__ __forceinline__ int first_key(int p, int chunk, int window) {
@@ -97,6 +98,15 @@ __device__ __forceinline__ int first_key(int p, int chunk, int window) {
 
 __device__ __forceinline__ float temperature(int p, float attn_scale, float floor_scale) {
   return attn_scale != 0.f ? 1.f + attn_scale * log1pf(floorf(((float)p + 1.f) / floor_scale)) : 1.f;
+}
+
+// 1 / (the row's sum with the sink's term), for outputs accumulated against the maximum m (base-2 scores).
+__device__ __forceinline__ float inverse_sum_with_sink(float m, float l, const float* sink, int h) {
+  if (!sink) return 1.f / l;
+  const float sk = sink[h] * 1.4426950408889634f;
+  const float mm = fmaxf(m, sk);
+  const float c = exp2f(m - mm);
+  return c / (l * c + exp2f(sk - mm));
 }
 
 // Loads keys [key0, key0 + KT) of request r, KV head hk, into ks / vs (each [KT][DH], swizzled).
@@ -510,7 +520,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   }
 }
 
-// out[n, h, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits in ascending order.
+// out[n, h, :] = sum_s o_s 2^(m_s - m) / (sum_s l_s 2^(m_s - m) + the sink's term, if any), splits in ascending order.
 // The splits' (m, l) pairs are fetched by as many threads at once and kept in shared memory; with more than
 // COMBINE_CACHE splits they are read from global memory again.
 #define COMBINE_CACHE 512
@@ -529,6 +539,7 @@ __global__ void attention_combine_kernel(const AttnParams P) {
   const float2* ml = reinterpret_cast<const float2*>(P.part_ml) + row;
   const bool cached = splits <= COMBINE_CACHE;
   float mm = NEG_BIG, ll = 0.f;
+  const float sink_log2 = P.sink ? P.sink[h] * 1.4426950408889634f : 0.f;  // a weight: read before the wait
   pdl_wait();
   if (cached) {
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
@@ -538,13 +549,17 @@ __global__ void attention_combine_kernel(const AttnParams P) {
     }
     __syncthreads();
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ms[s]);
+    if (P.sink) mm = fmaxf(mm, sink_log2);
     for (int s = 0; s < splits; ++s) ll += wgt[s] * exp2f(ms[s] - mm);
+    if (P.sink) ll += exp2f(sink_log2 - mm);
     __syncthreads();
     for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = exp2f(ms[s] - mm) / ll;
     __syncthreads();
   } else {
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ml[s].x);
+    if (P.sink) mm = fmaxf(mm, sink_log2);
     for (int s = 0; s < splits; ++s) ll += ml[s].y * exp2f(ml[s].x - mm);
+    if (P.sink) ll += exp2f(sink_log2 - mm);
   }
   const float* po = P.part_o + row * DH;
   for (int d = threadIdx.x; d < DH; d += blockDim.x) {
@@ -694,7 +709,7 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams
   cp_async_wait<0>();
   if (warp < G) {
     const int col = (lane & 3) * 2;
-    const float i0 = 1.f / l[0], i1 = 1.f / l[1];
+    const float i0 = inverse_sum_with_sink(m[0], l[0], P.sink, hk * G + warp), i1 = inverse_sum_with_sink(m[1], l[1], P.sink, hk * G + warp);
     bf16* o0 = P.out + ((size_t)(n0 + t0) * P.Hq + hk * G + warp) * DH;
     bf16* o1 = P.out + ((size_t)(n0 + t1) * P.Hq + hk * G + warp) * DH;
 #pragma unroll
@@ -884,7 +899,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
   if (!ok) return;
   {
     const int col = (lane & 3) * 2;
-    const float i0 = 1.f / l[0], i1 = 1.f / l[1];
+    const float i0 = inverse_sum_with_sink(m[0], l[0], P.sink, hk * G + warp), i1 = inverse_sum_with_sink(m[1], l[1], P.sink, hk * G + warp);
     bf16* o0 = P.out + ((size_t)(n0 + t0) * P.Hq + hk * G + warp) * DH;
     bf16* o1 = P.out + ((size_t)(n0 + t1) * P.Hq + hk * G + warp) * DH;
 #pragma unroll
@@ -898,7 +913,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
 // --------------------------------------------------------------------------------------- host
 static int fill_params(AttnParams& P, const void* q, const void* pages, const int* block_table, int bt_stride,
                        const int* req_of_token, const int* positions, void* out, int Hq, int Hkv, int dh, int page_size,
-                       int num_pages, float scale, int chunk, int window, float attn_scale, float floor_scale, int* status) {
+                       int num_pages, float scale, int chunk, int window, float attn_scale, float floor_scale, const float* sink,
+                       int* status) {
   JLX_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d query heads are no multiple of %d KV heads", Hq, Hkv);
   JLX_REQUIRE(dh == 64 || dh == 128, "attention_mma: head size %d is not built (64 and 128 are); use the generic kernel", dh);
   JLX_REQUIRE(page_size > 0 && num_pages > 0 && bt_stride > 0, "attention: bad cache sizes");
@@ -909,6 +925,7 @@ static int fill_params(AttnParams& P, const void* q, const void* pages, const in
   P.page_size = page_size; P.num_pages = num_pages; P.scale_log2 = scale * 1.4426950408889634f;
   P.chunk = chunk; P.window = window; P.attn_scale = attn_scale; P.floor_scale = floor_scale; P.status = status;
   P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0; P.split_keys = SPLIT_UNIT; P.rows = nullptr;
+  P.sink = sink;
   return 0;
 }
 
@@ -990,10 +1007,10 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
                                  const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv, int dh,
                                  int page_size, int num_pages, float scale, int chunk, int window, float attn_scale,
                                  float floor_scale, float* part_o, float* part_ml, int max_splits, int split_keys,
-                                 const int* rows, int* status, cudaStream_t stream) {
+                                 const int* rows, const float* sink, int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
-                  scale, chunk, window, attn_scale, floor_scale, status)) return 1;
+                  scale, chunk, window, attn_scale, floor_scale, sink, status)) return 1;
   JLX_REQUIRE(Hq / Hkv <= 16, "attention_decode: %d query heads per KV head; up to 16 are supported", Hq / Hkv);
   JLX_REQUIRE(part_o && part_ml && max_splits > 0, "attention_decode: scratch for the partial results is missing");
   JLX_REQUIRE(split_keys > 0 && split_keys % SPLIT_UNIT == 0, "attention_decode: split size %d is no multiple of %d", split_keys, SPLIT_UNIT);
@@ -1040,10 +1057,10 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
 JLX_API int jlx_attention_prefill(const void* q, const void* pages, const int* block_table, int bt_stride,
                                   const int* req_of_token, const int* positions, void* out, const int* tiles, int n_tiles,
                                   int Hq, int Hkv, int dh, int page_size, int num_pages, float scale, int chunk, int window,
-                                  float attn_scale, float floor_scale, int* status, cudaStream_t stream) {
+                                  float attn_scale, float floor_scale, const float* sink, int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
-                  scale, chunk, window, attn_scale, floor_scale, status)) return 1;
+                  scale, chunk, window, attn_scale, floor_scale, sink, status)) return 1;
   const int G = Hq / Hkv;
   JLX_REQUIRE(G <= 8, "attention_prefill: %d query heads per KV head; up to 8 are supported", G);
   JLX_REQUIRE(Hkv <= 65535, "attention_prefill: too many KV heads");

@@ -135,6 +135,7 @@ struct TcParams {
   int chunk, window;
   float attn_scale, floor_scale;
   int* status;
+  const float* sink;    // optional, [Hq]: one more term exp(sink[h]) in the softmax's denominator, without a value
 };
 
 __device__ __forceinline__ int first_key(int p, int chunk, int window) {
@@ -482,7 +483,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float total = 0.f;
 #pragma unroll
       for (int q = 0; q < PARTS; ++q) total += xsum[mp][q][row];
-      const float inv = 1.f / total;
+      float inv = 1.f / total;
+      if (P.sink) {  // the sink's term joins the sum; m is the reference point that the sums were taken against
+        const float sk = P.sink[it.head] * 1.4426950408889634f;
+        const float mm = fmaxf(m, sk);
+        const float c = exp2f(m - mm);
+        inv = c / (total * c + exp2f(sk - mm));
+      }
       bf16* dst = P.out + ((size_t)(it.n0 + row) * P.Hq + it.head) * DH;
       uint32_t v[32];
 #pragma unroll 1
@@ -544,7 +551,7 @@ JLX_API int jlx_attention_prefill_tc_supported(int Hq, int Hkv, int dh, int page
 JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int* block_table, int bt_stride,
                                      const int* req_of_token, const int* positions, void* out, const int* tiles,
                                      int n_tiles, int N, int Hq, int Hkv, int dh, int page_size, int num_pages, float scale,
-                                     int chunk, int window, float attn_scale, float floor_scale, int* status,
+                                     int chunk, int window, float attn_scale, float floor_scale, const float* sink, int* status,
                                      cudaStream_t stream) {
   JLX_REQUIRE(jlx_attention_prefill_tc_supported(Hq, Hkv, dh, page_size),
               "attention_prefill_tc: needs head size 128 and pages of a multiple of 64 tokens (got %d, %d)", dh, page_size);
@@ -582,7 +589,7 @@ JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int
   P.block_table = block_table; P.bt_stride = bt_stride; P.req_of_token = req_of_token; P.positions = positions;
   P.out = (bf16*)out; P.tiles = tiles; P.Hq = Hq; P.Hkv = Hkv; P.page_size = page_size; P.num_pages = num_pages;
   P.scale_log2 = scale * 1.4426950408889634f; P.chunk = chunk; P.window = window; P.attn_scale = attn_scale;
-  P.floor_scale = floor_scale; P.status = status;
+  P.floor_scale = floor_scale; P.status = status; P.sink = sink;
   const size_t smem = 5 * (size_t)TILE_BYTES + 1024;
   static bool cfg = false;
   if (!cfg) {

@@ -379,17 +379,23 @@ JLX_API int jlx_kv_store(const void* k, const void* v, void* pages, int dtype, c
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// The same pass for attention whose q and k are normed with a weight BEFORE the rotation, rotated in the "rotate half"
-// layout on their first rot_dims entries only, and whose values may have another size than its keys.
+// The same pass in a general form, for attention whose q and k are RMS-normed (with a weight or without) BEFORE or AFTER
+// the rotation, rotated on their first rot_dims entries only, in halves or in neighbouring pairs, and whose values may
+// have another size than its keys, or be the keys as projected.
 //
-//   q, k:  y = x / sqrt(mean(x^2) + eps) * w   over the head's dk entries (w: [dk], shared by the heads; null = no norm)
-//          (y_i, y_(i + rot/2)) <- (y_i cos a - y_(i + rot/2) sin a,  y_(i + rot/2) cos a + y_i sin a),
-//          a = position * inv_freq[i], i < rot / 2; entries from rot on pass unchanged.
+//   norm:   y = x / sqrt(mean(x^2) + eps) (* w)   over the head's dk entries (w: [dk], shared by the heads, or null)
+//   halves: (y_i, y_(i + rot/2)) <- (y_i cos a - y_(i + rot/2) sin a,  y_(i + rot/2) cos a + y_i sin a),
+//   pairs:  (y_2i, y_(2i + 1))   <- (y_2i cos a - y_(2i + 1) sin a,    y_(2i + 1) cos a + y_2i sin a),
+//           a = position * inv_freq[i], i < rot / 2; entries from rot on pass unchanged.
 //
 // The projected rows are float32 (split-K partials are added first) with the q heads from column 0, the k heads from
-// column k_col and the v heads (dv entries each) from column v_col.  q_out and the cache keep `dpad` entries per head:
-// keys, queries and values are padded with zeros up to it, so that one page layout and the attention kernels built
-// for equal sizes serve keys of one size and values of another.
+// column k_col and the v heads (dv entries each) from column v_col (v_col = k_col: the values are the keys as they
+// were projected).  q_out and the cache keep `dpad` entries per head: keys, queries and values are padded with zeros
+// up to it, so that one page layout and the attention kernels built for equal sizes serve keys of one size and values
+// of another.
+enum { ROPE_PAIRS_HALVES = 0, ROPE_PAIRS_INTERLEAVED = 1 };
+enum { ROPE_NORM_NONE = 0, ROPE_NORM_BEFORE = 1, ROPE_NORM_AFTER = 2 };
+
 struct RopeRowsView {
   const float* p;
   long long split_stride;
@@ -403,15 +409,16 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
                                           const int* __restrict__ block_table, int bt_stride, const int* __restrict__ req_of_token,
                                           const int* __restrict__ positions, const float* __restrict__ q_norm_w,
                                           const float* __restrict__ k_norm_w, float eps, const float* __restrict__ inv_freq,
-                                          int rot, int Hq, int Hkv, int dk, int dv, int dpad, int page_size, int num_pages,
-                                          int store, int* status) {
+                                          int rot, int pairing, int norm_mode, int Hq, int Hkv, int dk, int dv, int dpad,
+                                          int page_size, int num_pages, int store, int* status) {
   JLX_TL(TL_ROPE);
   pdl_launch_dependents_if_small();
-  extern __shared__ float buf[];  // [warps][max(dk, dv)]
+  extern __shared__ float buf[];  // [warps][2][max(dk, dv)]: a head's row as projected (and normed), and as rotated
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const size_t n = blockIdx.x;
   const int dmax = dk > dv ? dk : dv;
-  float* row = buf + warp * dmax;
+  float* row = buf + (size_t)warp * 2 * dmax;
+  float* turned = row + dmax;
   pdl_wait();
   const int pos = positions[n];
   const int half = rot >> 1;
@@ -427,7 +434,8 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
   const int heads = Hq + (store ? 2 * Hkv : 0);
   for (int hh = blockIdx.y * nwarp + warp; hh < heads; hh += gridDim.y * nwarp) {
     const bool is_q = hh < Hq, is_k = !is_q && hh < Hq + Hkv;
-    const int d = is_q || is_k ? dk : dv;
+    const bool qk = is_q || is_k;
+    const int d = qk ? dk : dv;
     const int col = is_q ? hh * dk : (is_k ? k_col + (hh - Hq) * dk : v_col + (hh - Hq - Hkv) * dv);
     T* dst;
     if (is_q) dst = q_out + (n * Hq + hh) * dpad;
@@ -441,23 +449,40 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
       ss = fmaf(s, s, ss);
     }
     const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
-    if ((is_q || is_k) && w) {
+    if (qk && norm_mode == ROPE_NORM_BEFORE) {
       ss = warp_sum(ss);
       const float rms = sqrtf(ss / (float)d + eps);
       __syncwarp();
-      for (int i = lane; i < d; i += 32) row[i] = row[i] / rms * w[i];
+      for (int i = lane; i < d; i += 32) row[i] = w ? row[i] / rms * w[i] : row[i] / rms;
+    }
+    __syncwarp();
+    float ss2 = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      float y = row[i];
+      if (qk && i < rot) {
+        // the entry's partner and which of the pair it is: (i, i + rot/2) side by side in halves, or (2j, 2j + 1)
+        const bool first = pairing == ROPE_PAIRS_INTERLEAVED ? !(i & 1) : i < half;
+        const int f = pairing == ROPE_PAIRS_INTERLEAVED ? i >> 1 : (first ? i : i - half);
+        const int partner = pairing == ROPE_PAIRS_INTERLEAVED ? i ^ 1 : (first ? i + half : i - half);
+        float sn, cs;
+        sincosf((float)pos * inv_freq[f], &sn, &cs);
+        y = first ? row[i] * cs - row[partner] * sn : row[i] * cs + row[partner] * sn;
+      }
+      turned[i] = y;
+      ss2 = fmaf(y, y, ss2);
+    }
+    float rms_turned = 1.f;
+    const bool after = qk && norm_mode == ROPE_NORM_AFTER;
+    if (after) {
+      ss2 = warp_sum(ss2);
+      rms_turned = sqrtf(ss2 / (float)d + eps);
     }
     __syncwarp();
     for (int i = lane; i < dpad; i += 32) {
       float y = 0.f;
       if (i < d) {
-        y = row[i];
-        if ((is_q || is_k) && i < rot) {
-          const int f = i < half ? i : i - half;
-          float sn, cs;
-          sincosf((float)pos * inv_freq[f], &sn, &cs);
-          y = i < half ? row[i] * cs - row[i + half] * sn : row[i] * cs + row[i - half] * sn;
-        }
+        y = turned[i];
+        if (after) y = w ? y / rms_turned * w[i] : y / rms_turned;
       }
       dst[i] = from_f32<T>(y);
     }
@@ -466,26 +491,30 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
 }
 
 // proj: float32 rows (see RopeRowsView; p points at the first q column).  pages: [P, 2, Hkv, page_size, dpad] or null.
+// pairing: which entries turn together; norm_mode: no q/k norm, before the rotation, or after it (a null weight: the
+// norm without one).  v_col == k_col with dv == dk stores the keys as projected (neither normed nor turned) as values.
 JLX_API int jlx_rope_half_kv_store(const RopeRowsView* proj, int k_col, int v_col, void* q_out, void* pages, int dtype,
                                    const int* block_table, int bt_stride, const int* req_of_token, const int* positions,
                                    const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rot,
-                                   int N, int Hq, int Hkv, int dk, int dv, int dpad, int page_size, int num_pages, int store,
-                                   int* status, cudaStream_t stream) {
+                                   int pairing, int norm_mode, int N, int Hq, int Hkv, int dk, int dv, int dpad, int page_size,
+                                   int num_pages, int store, int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && dk > 0 && dv > 0, "rope_half: bad sizes");
   JLX_REQUIRE(dpad >= dk && dpad >= dv, "rope_half: the padded head size %d is below the key or value size (%d, %d)", dpad, dk, dv);
   JLX_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk, "rope_half: %d rotated entries of %d", rot, dk);
   JLX_REQUIRE(rot == 0 || inv_freq, "rope_half: frequencies missing");
+  JLX_REQUIRE(pairing == ROPE_PAIRS_HALVES || pairing == ROPE_PAIRS_INTERLEAVED, "rope_half: unknown pairing %d", pairing);
+  JLX_REQUIRE(norm_mode >= ROPE_NORM_NONE && norm_mode <= ROPE_NORM_AFTER, "rope_half: unknown norm mode %d", norm_mode);
   JLX_REQUIRE(!store || (pages && block_table && page_size > 0 && num_pages > 0), "rope_half: cache missing");
   if (N == 0) return 0;
   const int heads = Hq + (store ? 2 * Hkv : 0);
   const int nwarp = heads < 8 ? heads : 8;
   const int by = N >= 64 ? 1 : (heads + nwarp - 1) / nwarp;
-  const size_t smem = sizeof(float) * (size_t)nwarp * (dk > dv ? dk : dv);
+  const size_t smem = sizeof(float) * 2 * (size_t)nwarp * (dk > dv ? dk : dv);
   JLX_REQUIRE(smem <= 48 * 1024, "rope_half: head size too large");
   JLX_DISPATCH_DTYPE(dtype, T, {
     JLX_CUDA(jlx_launch_pdl(rope_half_kv_store_kernel<T>, dim3(N, by), dim3(nwarp * 32), smem, stream, *proj, k_col, v_col,
                             (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token, positions, q_norm_w, k_norm_w, eps,
-                            inv_freq, rot, Hq, Hkv, dk, dv, dpad, page_size, num_pages, store, status));
+                            inv_freq, rot, pairing, norm_mode, Hq, Hkv, dk, dv, dpad, page_size, num_pages, store, status));
   });
   JLX_LAUNCH_CHECK("rope_half_kv_store");
   return 0;
@@ -495,8 +524,8 @@ JLX_API int jlx_rope_half_kv_store(const RopeRowsView* proj, int k_col, int v_co
 // which dv count) through a gate per token and head, into (a column range of) the rows that the output product reads.
 // gate: float32 rows, possibly split-K partials (p null: no gate).
 template <typename T>
-__global__ void head_gate_kernel(const T* __restrict__ attn, RopeRowsView gate, float mult, T* __restrict__ out, long long ld_out,
-                                 int Hq, int dv, int dpad) {
+__global__ void head_gate_kernel(const T* __restrict__ attn, RopeRowsView gate, int per_channel, float mult, T* __restrict__ out,
+                                 long long ld_out, int Hq, int dv, int dpad) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
   pdl_wait();
@@ -506,21 +535,21 @@ __global__ void head_gate_kernel(const T* __restrict__ attn, RopeRowsView gate, 
     float g = mult;
     if (gate.p) {
       float s = 0.f;
-      for (int z = 0; z < gate.splits; ++z) s += gate.p[(size_t)z * gate.split_stride + n * gate.ld + hd];
+      for (int z = 0; z < gate.splits; ++z) s += gate.p[(size_t)z * gate.split_stride + n * gate.ld + (per_channel ? idx : hd)];
       g *= 1.f / (1.f + expf(-s));
     }
     out[n * ld_out + idx] = from_f32<T>(g * to_f32<T>(attn[(n * Hq + hd) * dpad + c]));
   }
 }
 
-JLX_API int jlx_head_gate(const void* attn, const RopeRowsView* gate, float mult, void* out, int dtype, long long ld_out, int N,
-                          int Hq, int dv, int dpad, cudaStream_t stream) {
+JLX_API int jlx_head_gate(const void* attn, const RopeRowsView* gate, int per_channel, float mult, void* out, int dtype,
+                          long long ld_out, int N, int Hq, int dv, int dpad, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && dv > 0 && dpad >= dv && ld_out >= (long long)Hq * dv, "head_gate: bad sizes");
   if (N == 0) return 0;
   RopeRowsView none = {nullptr, 0, 0, 1, 0};
   JLX_DISPATCH_DTYPE(dtype, T, {
     JLX_CUDA(jlx_launch_pdl(head_gate_kernel<T>, dim3(N), dim3(Hq * dv >= 1024 ? 256 : 128), 0, stream, (const T*)attn,
-                            gate ? *gate : none, mult, (T*)out, ld_out, Hq, dv, dpad));
+                            gate ? *gate : none, per_channel, mult, (T*)out, ld_out, Hq, dv, dpad));
   });
   JLX_LAUNCH_CHECK("head_gate");
   return 0;

@@ -513,36 +513,101 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor | None, per_head: bool,
          c_int(H), c_int(dv), _stream())
 
 
+# ------------------------------------------------------------------------------ the gated delta rule
+CONV_ACTIVATIONS = {"none": 0, "silu": 1}  # csrc/delta_rule.cu
+
+
+def conv_unit_prep(proj: _RowsView, b_col: int, a_col: int, conv_w: torch.Tensor, conv_state: torch.Tensor | None,
+                   rate_log: torch.Tensor, a_bias: torch.Tensor, cu_q: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor,
+                   req_of_token: torch.Tensor, positions: torch.Tensor, qo: torch.Tensor, ko: torch.Tensor, vo: torch.Tensor,
+                   beta: torch.Tensor, decay: torch.Tensor, activation: str, unit_eps: float, q_scale: float) -> None:
+    """From projected float32 rows whose first C = 2 G dk + H dv columns are the q, k and v channels: each channel
+    through a short causal convolution over its request's time axis (``conv_w`` float32 [C, taps], the last column the
+    current token's; ``conv_state`` float32 [slots, taps - 1, C] = a request's last inputs, read and moved on) and the
+    activation; q and k heads made unit vectors, x / sqrt(sum x^2 + unit_eps), q times ``q_scale``; beta = sigmoid of
+    the H columns from ``b_col``; decay = exp(-exp(rate_log) * softplus(columns from a_col + a_bias)).
+    qo, ko: float32 [N, G, dk]; vo: [N, H, dv]; beta, decay: [N, H]."""
+    _contig(conv_w, conv_state, rate_log, a_bias, qo, ko, vo, beta, decay)
+    N, G, dk = qo.shape
+    _, H, dv = vo.shape
+    C, taps = conv_w.shape
+    if any(t.dtype != torch.float32 for t in (conv_w, rate_log, a_bias, qo, ko, vo, beta, decay)) or \
+            (conv_state is not None and conv_state.dtype != torch.float32):
+        raise KernelError("conv_unit_prep: everything is float32")
+    if C != 2 * G * dk + H * dv or rate_log.numel() != H or a_bias.numel() != H or tuple(beta.shape) != (N, H) \
+            or tuple(decay.shape) != (N, H) or (conv_state is not None and tuple(conv_state.shape[1:]) != (taps - 1, C)):
+        raise KernelError(f"conv_unit_prep: shapes do not fit: conv {tuple(conv_w.shape)} for {G} x {dk} keys and {H} x {dv} values")
+    _run("delta_rule", "jlx_conv_unit_prep", ctypes.byref(proj), c_int(b_col), c_int(a_col), _ptr(conv_w), _ptr(conv_state),
+         _ptr(rate_log), _ptr(a_bias), _ptr(cu_q), _ptr(q_start), _ptr(slot_ids), _ptr(req_of_token), _ptr(positions), _ptr(qo),
+         _ptr(ko), _ptr(vo), _ptr(beta), _ptr(decay), c_int(N), c_int(slot_ids.numel()), c_int(G), c_int(H), c_int(dk), c_int(dv),
+         c_int(taps), c_int(CONV_ACTIVATIONS[activation]), c_float(unit_eps), c_float(q_scale), _stream())
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, o: torch.Tensor) -> None:
+    """Over each request's tokens, in order:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+    q, k: float32 [N, G, dk] (head h reads key head h // (H / G)); v, o: [N, H, dv]; beta, decay: [N, H];
+    state: float32 [slots, H, dk, dv]."""
+    _contig(q, k, v, beta, decay, state, o)
+    N, G, dk = q.shape
+    _, H, dv = v.shape
+    if any(t.dtype != torch.float32 for t in (q, k, v, beta, decay, state, o)):
+        raise KernelError("delta_scan: everything is float32")
+    if tuple(state.shape[1:]) != (H, dk, dv) or tuple(o.shape) != (N, H, dv) or tuple(k.shape) != (N, G, dk) or H % G:
+        raise KernelError(f"delta_scan: shapes do not fit: q {tuple(q.shape)}, v {tuple(v.shape)}, state {tuple(state.shape)}")
+    _run("delta_rule", "jlx_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(cu_q), _ptr(slot_ids),
+         _ptr(o), c_int(slot_ids.numel()), c_int(G), c_int(H), c_int(dk), c_int(dv), _stream())
+
+
 # ---------------------------------- weighted q/k norm + rotate-half rotation + page write; gated attention heads
-def rope_half_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
+ROPE_PAIRINGS = {"halves": 0, "pairs": 1}  # csrc/rope_kv.cu
+ROPE_NORMS = {"none": 0, "before": 1, "after": 2}
+
+
+def rope_norm_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
                        block_table: torch.Tensor | None, req_of_token: torch.Tensor, positions: torch.Tensor,
                        q_norm_weight: torch.Tensor | None, k_norm_weight: torch.Tensor | None, eps: float,
-                       inv_freq: torch.Tensor | None, rot_dims: int, Hq: int, Hkv: int, dk: int, dv: int, status: torch.Tensor) -> None:
+                       inv_freq: torch.Tensor | None, rot_dims: int, Hq: int, Hkv: int, dk: int, dv: int, status: torch.Tensor,
+                       pairing: str = "halves", norm: str = "before") -> None:
     """From projected float32 rows (q heads from the view's first column, k heads from column k_col, v heads of dv
-    entries from v_col): q and k RMS-normed over dk with a weight, then their first rot_dims entries rotated (entry i
-    paired with i + rot_dims / 2); q into q_out [N, Hq, dpad], k and v into the token's cache row
-    (pages [P, 2, Hkv, page_size, dpad]), all padded with zeros to dpad."""
+    entries from v_col; v_col = k_col stores the keys as projected as values): q and k RMS-normed over dk (``norm``:
+    "none", "before" or "after" the rotation; with a weight where one is given), their first rot_dims entries rotated
+    (``pairing`` "halves": entry i with i + rot_dims / 2; "pairs": entry 2i with 2i + 1); q into q_out [N, Hq, dpad],
+    k and v into the token's cache row (pages [P, 2, Hkv, page_size, dpad]), all padded with zeros to dpad."""
     _contig(q_out, pages, block_table, q_norm_weight, k_norm_weight, inv_freq)
     N, _, dpad = q_out.shape
     store = pages is not None
     if store and (pages.dtype != q_out.dtype or tuple(pages.shape[1:3]) != (2, Hkv) or pages.shape[4] != dpad):
-        raise KernelError(f"rope_half_kv_store: pages {tuple(pages.shape)} do not fit {Hkv} heads padded to {dpad}")
+        raise KernelError(f"rope_norm_kv_store: pages {tuple(pages.shape)} do not fit {Hkv} heads padded to {dpad}")
     _run("rope_kv", "jlx_rope_half_kv_store", ctypes.byref(proj), c_int(k_col), c_int(v_col), _ptr(q_out), _ptr(pages),
          c_int(code(q_out.dtype)), _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token),
-         _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims), c_int(N),
-         c_int(Hq), c_int(Hkv), c_int(dk), c_int(dv), c_int(dpad), c_int(pages.shape[3] if store else 0),
-         c_int(pages.shape[0] if store else 0), c_int(int(store)), _ptr(status), _stream())
+         _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims),
+         c_int(ROPE_PAIRINGS[pairing]), c_int(ROPE_NORMS[norm]), c_int(N), c_int(Hq), c_int(Hkv), c_int(dk), c_int(dv), c_int(dpad),
+         c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0), c_int(int(store)), _ptr(status), _stream())
 
 
-def head_gate(attn: torch.Tensor, gate: _RowsView | None, mult: float, out: torch.Tensor, dv: int) -> None:
-    """out[n, h dv + c] = mult * sigmoid(gate[n, h]) * attn[n, h, c] for c < dv.  attn: [N, Hq, dpad]; gate: float32
-    projected rows (None: no gate); out: [N, Hq dv], possibly a column range of wider rows."""
+def rope_half_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
+                       block_table: torch.Tensor | None, req_of_token: torch.Tensor, positions: torch.Tensor,
+                       q_norm_weight: torch.Tensor | None, k_norm_weight: torch.Tensor | None, eps: float,
+                       inv_freq: torch.Tensor | None, rot_dims: int, Hq: int, Hkv: int, dk: int, dv: int, status: torch.Tensor) -> None:
+    """:func:`rope_norm_kv_store` in the form "a weighted norm (where both weights are given) before a rotation in halves"."""
+    if (q_norm_weight is None) != (k_norm_weight is None):
+        raise KernelError("rope_half_kv_store: q and k are normed both or neither")
+    rope_norm_kv_store(proj, k_col, v_col, q_out, pages, block_table, req_of_token, positions, q_norm_weight, k_norm_weight, eps,
+                       inv_freq, rot_dims, Hq, Hkv, dk, dv, status, "halves", "none" if q_norm_weight is None else "before")
+
+
+def head_gate(attn: torch.Tensor, gate: _RowsView | None, mult: float, out: torch.Tensor, dv: int, per_channel: bool = False) -> None:
+    """out[n, h dv + c] = mult * sigmoid(gate[n, h]) * attn[n, h, c] for c < dv (``per_channel``: gate[n, h dv + c], a gate
+    for every output channel).  attn: [N, Hq, dpad]; gate: float32 projected rows (None: no gate); out: [N, Hq dv],
+    possibly a column range of wider rows."""
     _contig(attn)
     N, Hq, dpad = attn.shape
     if out.shape != (N, Hq * dv) or out.stride(1) != 1 or out.dtype != attn.dtype:
         raise KernelError("head_gate: out must be [N, Hq * dv] of the attention's type with contiguous rows")
-    _run("rope_kv", "jlx_head_gate", _ptr(attn), ctypes.byref(gate) if gate is not None else None, c_float(mult), _ptr(out),
-         c_int(code(attn.dtype)), c_longlong(out.stride(0) if N > 1 else Hq * dv), c_int(N), c_int(Hq), c_int(dv), c_int(dpad), _stream())
+    _run("rope_kv", "jlx_head_gate", _ptr(attn), ctypes.byref(gate) if gate is not None else None, c_int(int(per_channel)),
+         c_float(mult), _ptr(out), c_int(code(attn.dtype)), c_longlong(out.stride(0) if N > 1 else Hq * dv), c_int(N), c_int(Hq),
+         c_int(dv), c_int(dpad), _stream())
 
 
 # ------------------------------------------------------------------- position encoding + cache
@@ -574,9 +639,11 @@ def kv_store(k: torch.Tensor, v: torch.Tensor, pages: torch.Tensor, block_table:
 # ---------------------------------------------------------------------------------- attention
 def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                       positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int,
-                      attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
-    """q: [N, Hq, dh]; pages: [P, 2, Hkv, page, dh]; out: [N, Hq, dh]."""
+                      attn_scale: float, floor_scale: float, status: torch.Tensor, sink: torch.Tensor | None = None) -> None:
+    """q: [N, Hq, dh]; pages: [P, 2, Hkv, page, dh]; out: [N, Hq, dh].  ``sink``: float32 [Hq] or None; with it the
+    softmax's denominator has one more term exp(sink[h]) that carries no value (all four attention kernels take it)."""
     _contig(q, pages, block_table, out)
+    _check_sink(sink, q.shape[1])
     N, Hq, dh = q.shape
     P, _, Hkv, page_size, dh2 = pages.shape
     if dh2 != dh or pages.dtype != q.dtype:
@@ -584,7 +651,12 @@ def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.T
     _run("attention_generic", "jlx_attention_generic", _ptr(q), _ptr(pages), c_int(code(q.dtype)), _ptr(block_table),
          c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv),
          c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
+
+
+def _check_sink(sink: torch.Tensor | None, Hq: int) -> None:
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != Hq or not sink.is_contiguous()):
+        raise KernelError(f"attention: the sink must be float32 [{Hq}], one number per query head")
 
 
 def attention_mma_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, decode: bool) -> bool:
@@ -603,13 +675,15 @@ def attention_decode_plan(max_kv_len: int, chunk: int, window: int, pairs: int) 
 def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int, attn_scale: float,
                      floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int, split_keys: int,
-                     status: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int = 0) -> None:
+                     status: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int = 0,
+                     sink: torch.Tensor | None = None) -> None:
     """Split-KV attention for one query token per request (tensor cores, bfloat16).
     part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2].
     rows / n_rows: work on these token rows only (int32, the first n_rows entries): the single decoded tokens of
     a step that also holds prompt portions; N is then n_rows."""
     _contig(q, pages, block_table, out, part_o, part_ml, rows)
     N, Hq, dh = q.shape
+    _check_sink(sink, Hq)
     if rows is not None:
         N = n_rows
     P, _, Hkv, page_size, _ = pages.shape
@@ -618,21 +692,23 @@ def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Te
     _run("attention_mma", "jlx_attention_decode", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size),
          c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale), c_float(floor_scale), _ptr(part_o),
-         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(rows), _ptr(status), _stream())
+         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(rows), _ptr(sink), _ptr(status), _stream())
 
 
 def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                       positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
-                      chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
+                      chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor,
+                      sink: torch.Tensor | None = None) -> None:
     """Flash attention over the paged cache for prompt portions (tensor cores, bfloat16).
     tiles: int32 [n_tiles, 2] = (first token row, count <= 16), each within one request."""
     _contig(q, pages, block_table, out, tiles)
     N, Hq, dh = q.shape
+    _check_sink(sink, Hq)
     P, _, Hkv, page_size, _ = pages.shape
     _run("attention_mma", "jlx_attention_prefill", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(Hq), c_int(Hkv), c_int(dh),
          c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
 
 
 def attention_prefill_tc_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, page_size: int) -> bool:
@@ -643,17 +719,19 @@ def attention_prefill_tc_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: 
 
 def attention_prefill_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                          positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
-                         chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
+                         chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor,
+                         sink: torch.Tensor | None = None) -> None:
     """Flash attention for prompt portions on tcgen05 (bfloat16, head size 128, pages of a multiple of 64).
     tiles: int32 [n_tiles, 2] = (first token row, count <= 128), each within one request; only the rows
     of these tiles are written."""
     _contig(q, pages, block_table, out, tiles)
     N, Hq, dh = q.shape
+    _check_sink(sink, Hq)
     P, _, Hkv, page_size, _ = pages.shape
     _run("attention_tc", "jlx_attention_prefill_tc", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(N), c_int(Hq), c_int(Hkv),
          c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
 
 
 # ------------------------------------------------------------------------------------- GEMMs

@@ -50,6 +50,8 @@ class PagedAttention(Mixer):
     ``chunk``: query and key must lie in the same chunk of that many positions (model.py:738-740);
     ``window``: keys within the last that many positions; None = no such limit.
     ``qk_norm_eps``: eps of the weightless norm of q and k, None = no norm.
+    ``sink``: [Hq] or None; with it the softmax's denominator has one more term exp(sink[h]) that carries no value
+    (zeros: "one added to the denominator").
     A layer with ``shares_cache`` projects only q and reads pages that another layer wrote.
     """
 
@@ -58,9 +60,10 @@ class PagedAttention(Mixer):
 
     def __init__(self, w_qkv: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PositionEncoding, qk_norm_eps: float | None = None, chunk: int | None = None,
-                 window: int | None = None, scale: float | None = None):
+                 window: int | None = None, scale: float | None = None, sink: torch.Tensor | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} KV heads")
+        self.sink = self._sink_vector(sink, n_heads)
         rows = (n_heads + 2 * n_kv_heads) * head_dim
         if w_qkv.shape[0] != rows or w_o.shape[1] != n_heads * head_dim or w_o.shape[0] != w_qkv.shape[1]:
             raise ValueError(f"attention weights do not fit: w_qkv {tuple(w_qkv.shape)}, w_o {tuple(w_o.shape)} for "
@@ -71,6 +74,16 @@ class PagedAttention(Mixer):
         self.qk_norm_eps = qk_norm_eps
         self.chunk, self.window = chunk, window
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)  # model.py:774
+
+    sink: torch.Tensor | None = None
+
+    @staticmethod
+    def _sink_vector(sink, n_heads: int) -> torch.Tensor | None:
+        if sink is None:
+            return None
+        if sink.numel() != n_heads:
+            raise ValueError(f"the sink has {sink.numel()} entries for {n_heads} query heads")
+        return sink.to(torch.float32).contiguous()
 
     # Head sizes that the tensor-core attention kernels are built for: a model with another head size never
     # asks for them (and so never compiles them).
@@ -119,7 +132,7 @@ class PagedAttention(Mixer):
         part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
         K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
                            chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status,
-                           rows, n_rows)
+                           rows, n_rows, self.sink)
 
     def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
         """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV for
@@ -145,35 +158,38 @@ class PagedAttention(Mixer):
                     # long portions on the tcgen05 kernel (128-token tiles), the short ones below
                     K.attention_prefill_tc(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
                                            ctx.arrays["attn_tiles_long"], count["attn_tiles_long"], self.scale, chunk, window,
-                                           attn_scale, floor_scale, ctx.status)
+                                           attn_scale, floor_scale, ctx.status, self.sink)
                     tiles, n_tiles = ctx.arrays["attn_tiles_short"], count["attn_tiles_short"]
                     kinds = ("tc", "flash" if n_tiles else "", "split_kv" if count["attn_single_rows"] else "")
                     ctx.scratch.setdefault("attention_kernels", set()).add(tuple(k for k in kinds if k))
                 if n_tiles:
                     K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, tiles,
-                                        n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status)
+                                        n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status, self.sink)
                 return
         K.attention_generic(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
-                            self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status)
+                            self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status, self.sink)
 
 
 register_part("mixer", "paged_attention", PagedAttention)
 
 
 class GatedPagedAttention(ProjectedMixer, PagedAttention):
-    """Grouped-query softmax attention over the paged cache whose queries and keys are RMS-normed with a weight BEFORE
-    they are rotated, rotated on their first ``rot_dims`` entries only in the rotate-half layout (entry i pairs with
-    i + rot_dims / 2, angle position * rot_base^(-2i / rot_dims)), whose values may have another size than its keys, and
-    whose heads pass a sigmoid gate, one number per token and head, before the output product:
+    """Grouped-query softmax attention over the paged cache in a general form: queries and keys RMS-normed over the head
+    (with a weight or without; BEFORE or AFTER the rotation; or not at all), rotated on their first ``rot_dims`` entries
+    only (``pairing`` "halves": entry i with i + rot_dims / 2, the rotate-half layout; "pairs": entry 2i with 2i + 1;
+    angle position * inv_freq[i]), values of another size than keys, or the keys themselves as projected
+    (``values_are_keys``: no value projection), an optional sink in the softmax, and a sigmoid gate on the heads'
+    outputs before the output product, one number per token and head (``gate`` "head") or per output channel ("channel"):
 
         out = W_o [ sigmoid(W_g h)_a * softmax(scale * q_a K^T) V  for every head a ]
 
-    ``w_in``: [Hq dk + Hkv dk + Hkv dv (+ Hq), D] = the q, k, v and gate projections stacked in that order (no gate rows:
-    no gate).  ``q_norm_weight`` / ``k_norm_weight``: [dk], shared by the heads; None = no norm.  ``window``: a query
-    sees itself and the window - 1 positions before it.  Keys, queries and values are kept at one padded size
-    (``padded_dim`` >= max(dk, dv), zeros beyond their own): one page layout, and the attention kernels built for
-    equal sizes, serve both.  It is a :class:`ProjectedMixer`: beside another mixer that reads the same input, both
-    share their input and output products."""
+    ``w_in``: the q, k, v and gate projections stacked in that order, [Hq dk + Hkv dk + Hkv dv + gate rows, D] (no v rows
+    with ``values_are_keys``; gate rows: Hq, Hq dv or none).  ``q_norm_weight`` / ``k_norm_weight``: [dk], shared by the
+    heads.  ``norm``: "before", "after" or "none"; None = "before" if a weight is given, else "none".  ``window``: a query
+    sees itself and the window - 1 positions before it; ``chunk``: the positions of its own chunk.  Keys, queries and
+    values are kept at one padded size (``padded_dim`` >= max(dk, dv), zeros beyond their own): one page layout, and the
+    attention kernels built for equal sizes, serve both.  It is a :class:`ProjectedMixer`: beside another mixer that
+    reads the same input, both share their input and output products."""
 
     kernel_libraries = ("attention_generic", "gemm_simt", "rope_kv")
     kernel_libraries_bf16 = ("attention_mma", "attention_tc", "gemm_stream")
@@ -181,18 +197,31 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
     def __init__(self, w_in: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
                  scale: float, eps: float, q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
                  inv_freq: torch.Tensor | None = None, rot_dims: int = 0, window: int | None = None, chunk: int | None = None,
-                 gated: bool = True, padded_dim: int | None = None):
+                 gated: bool = True, padded_dim: int | None = None, sink: torch.Tensor | None = None, pairing: str = "halves",
+                 norm: str | None = None, values_are_keys: bool = False, gate: str | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} KV heads")
-        rows = (n_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim + (n_heads if gated else 0)
+        gate = ("head" if gated else "none") if gate is None else gate
+        if gate not in ("none", "head", "channel") or pairing not in K.ROPE_PAIRINGS:
+            raise ValueError(f"gate {gate!r} (none, head, channel) or pairing {pairing!r} (halves, pairs) is unknown")
+        if values_are_keys and value_dim != head_dim:
+            raise ValueError(f"values that are the keys have the keys' size {head_dim}, not {value_dim}")
+        gate_rows = {"none": 0, "head": n_heads, "channel": n_heads * value_dim}[gate]
+        rows = (n_heads + n_kv_heads) * head_dim + (0 if values_are_keys else n_kv_heads * value_dim) + gate_rows
         if w_in.shape[0] != rows or w_o.shape[1] != n_heads * value_dim or w_o.shape[0] != w_in.shape[1]:
             raise ValueError(f"attention weights do not fit: w_in {tuple(w_in.shape)}, w_o {tuple(w_o.shape)} for {n_heads}/"
-                             f"{n_kv_heads} heads of {head_dim} (values {value_dim}){' with a gate' if gated else ''}")
+                             f"{n_kv_heads} heads of {head_dim} (values {value_dim}{', the keys' if values_are_keys else ''}) "
+                             f"with gate {gate!r}")
         if rot_dims % 2 or not 0 <= rot_dims <= head_dim or (rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2)):
             raise ValueError(f"{rot_dims} rotated entries of {head_dim} need {rot_dims // 2} frequencies")
         for w in (q_norm_weight, k_norm_weight):
             if w is not None and w.numel() != head_dim:
                 raise ValueError(f"a q/k norm weight has {w.numel()} entries for heads of {head_dim}")
+        if (q_norm_weight is None) != (k_norm_weight is None):
+            raise ValueError("q and k are normed with a weight each, or both without")
+        self.norm = ("none" if q_norm_weight is None else "before") if norm is None else norm
+        if self.norm not in K.ROPE_NORMS:
+            raise ValueError(f"norm {norm!r} is unknown (none, before, after)")
         self.w_in, self.w_o = w_in, w_o
         self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim = n_heads, n_kv_heads, head_dim, value_dim
         self.head_dim = max(head_dim, value_dim) if padded_dim is None else int(padded_dim)  # what the cache and the kernels see
@@ -200,8 +229,10 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
             raise ValueError(f"padded size {self.head_dim} is below the key or value size")
         f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
         self.q_norm_weight, self.k_norm_weight, self.inv_freq = f32(q_norm_weight), f32(k_norm_weight), f32(inv_freq)
-        self.rot_dims, self.eps, self.gated = int(rot_dims), float(eps), gated
+        self.rot_dims, self.eps, self.gate, self.gated = int(rot_dims), float(eps), gate, gate != "none"
+        self.pairing, self.values_are_keys = pairing, bool(values_are_keys)
         self.chunk, self.window, self.scale = chunk, window, float(scale)
+        self.sink = self._sink_vector(sink, n_heads)
         self.position, self.qk_norm_eps = None, None
 
     @staticmethod
@@ -221,17 +252,20 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
     def core(self, ctx: StepContext, h, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
         Hq, Hkv, dk, dv = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
         n = proj.data.shape[-2]
+        k_col = Hq * dk
+        v_col = k_col if self.values_are_keys else k_col + Hkv * dk  # the keys as projected stand in for values
+        gate_col = v_col + (Hkv * dk if self.values_are_keys else Hkv * dv)
         q = torch.empty((n, Hq, self.head_dim), dtype=ctx.runtime.dtype, device=out.device)
         with scope("rope"):
-            K.rope_half_kv_store(K.rows_view(proj.data, proj.splits, col), Hq * dk, (Hq + Hkv) * dk, q,
+            K.rope_norm_kv_store(K.rows_view(proj.data, proj.splits, col), k_col, v_col, q,
                                  cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
                                  ctx.req_of_token, ctx.positions, self.q_norm_weight, self.k_norm_weight, self.eps,
-                                 self.inv_freq, self.rot_dims, Hq, Hkv, dk, dv, ctx.status)
+                                 self.inv_freq, self.rot_dims, Hq, Hkv, dk, dv, ctx.status, self.pairing, self.norm)
         attn = torch.empty_like(q)
         with scope("attention"):
             self.attend(ctx, q, cache, attn, 0.0, 1.0)
-            gate = K.rows_view(proj.data, proj.splits, col + (Hq + Hkv) * dk + Hkv * dv) if self.gated else None
-            K.head_gate(attn, gate, mult, out, dv)
+            gate = K.rows_view(proj.data, proj.splits, col + gate_col) if self.gated else None
+            K.head_gate(attn, gate, mult, out, dv, per_channel=self.gate == "channel")
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache):
         return ProjectedMixer.forward(self, ctx, h, cache)

@@ -12,19 +12,24 @@ class PreNormBlock(Block):
     """x += mixer(norm1(x)); x += feed_forward(norm2(x))  (llama4/llama4_jax/model.py:1156-1183).
 
     The residual sums are done in float32 inside the following norm's kernel: a block returns its
-    last delta unadded, and the next block's first norm (or the model's final norm) adds it."""
+    last delta unadded, and the next block's first norm (or the model's final norm) adds it.
+    The feed-forward (with norm2) may be missing: the block is then its first sublayer alone."""
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None = None, feed_forward: FeedForward | None = None):
+        if (feed_forward is None) != (norm2 is None):
+            raise ValueError("a feed-forward comes with its norm, or not at all")
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
     def sub_parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache) -> torch.Tensor:
         dt = ctx.runtime.dtype
         with scope("attn_pre_norm"):  # the reference's names (model.py:1169-1180); each norm also adds the residual
             h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
         a = self.mixer.forward(ctx, h, cache)
+        if self.feed_forward is None:
+            return a
         want32 = self.feed_forward.needs_f32_input
         router = self.feed_forward.router_request() if self.norm2.fuses_router else None
         with scope("attn_post_norm"):
@@ -167,5 +172,38 @@ class ReinjectionBlock(Block):
         return None
 
 
+class EmbeddingReentryBlock(Block):
+    """Adds the embedding's output to the stream once more:  x <- x + x0,  x0 = what the embedding put out for the token
+    (scaled as the embedding scales it).  It stands in front of every pass but the first of a stretch of layers that
+    runs several times.  It has no weights, mixes nothing across tokens and keeps no cache or state, and it launches
+    nothing: x0 joins the pending delta as one more term of the sum that the next norm's kernel adds to x."""
+
+    mixer = None
+    wants_embedding_output = True
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache):
+        from ..kernels import api as K
+        from .base import Rows, RowSum, as_rows
+
+        x0 = ctx.scratch["embedding_output"]
+        if isinstance(delta, RowSum):
+            terms, before = list(delta.terms), delta.materialize
+        else:
+            d = as_rows(delta)
+            terms, before = ([] if d is None else [d]), None
+
+        def materialize() -> torch.Tensor:
+            if before is not None:
+                return before() + x0
+            if not terms:
+                return x0
+            out = torch.empty_like(x0)
+            K.bias_act(terms[0].data, out, None, x0, "none", terms[0].splits)  # the partials in order, then x0
+            return out
+
+        return RowSum(terms + [Rows(x0, 1)], materialize)
+
+
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "reinjection", ReinjectionBlock)
+register_part("block", "embedding_reentry", EmbeddingReentryBlock)

@@ -32,6 +32,22 @@ def llama3_scaled_frequencies(head_dim: int, theta: float, scaling: dict | None)
     return scaled
 
 
+def wavelength_scaled_frequencies(base: float, dims: int, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Rotary frequencies f_i = base^(-2i / dims), i < dims / 2, rescaled by wavelength l = 2 pi / f: kept where
+    l < original / high, divided by ``factor`` where l > original / low, and between the two blended,
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  Evaluated in float64 and rounded once to
+    float32 (the same rule as :func:`llama3_scaled_frequencies`, with the constants as plain arguments)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    wavelength = 2.0 * math.pi / f
+    out = torch.where(wavelength > original / low, f / factor, f)
+    if high != low:
+        s = (original / wavelength - low) / (high - low)
+        between = ~(wavelength < original / high) & ~(wavelength > original / low)
+        out = torch.where(between, (1.0 - s) * f / factor + s * f, out)
+    return out.to(torch.float32)
+
+
 class _FusedEncoding(PositionEncoding):
     kernel_libraries = ("rope_kv",)
     accepts_partials = True
