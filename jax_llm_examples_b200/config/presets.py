@@ -123,6 +123,38 @@ PRESETS["makisun_tiny"] = {
         {"type": "wkv", "mixer": {"heads": 4, "dim": 8, "decay_rank": 8}, "mlp": None},
     ],
 }
+def vofusun_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 32768) -> dict[str, Any]:
+    """A Vofusun configuration at the layer sizes of a real model: windowed attention with a sink (head size 128, four
+    query heads per key head, a window of 1024, no rotation), the gated delta rule (state 128 x 128 per head, two heads
+    per key head, convolutions over 4 tokens) and chunked, gated attention whose keys are its values (chunks of 2048,
+    the whole head rotated in pairs with wavelength-scaled frequencies) in turn; a dense feed-forward in every layer."""
+    kv = max(heads // 4, 1)
+    kinds = [
+        {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5}},
+        {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(heads // 2, 1), "dim": 128, "vdim": 128, "conv": 4}},
+        {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "mask": {"size": 2048}, "scale": 1.0 / 128,
+                                          "rot": {"base": 500000.0, "dims": 128,
+                                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}},
+    ]
+    return {"architecture": "Vofusun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [dict(kinds[i % 3], mlp={"kind": "dense", "ff": ff}) for i in range(layers)]}
+
+
+# Vofusun, tiny: a looped stretch (layers 1 and 2, twice), a layer without a feed-forward, part of the head rotated.
+PRESETS["vofusun_tiny"] = {
+    "architecture": "Vofusun", "vocab": 256, "width": 64, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "mask": {"size": 24}, "scale": 0.25}},
+        {"type": "delta", "mlp": None, "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 8, "conv": 3}},
+        {"type": "attention_2", "mlp": {"kind": "dense", "ff": 64},
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "mask": {"size": 40}, "scale": 0.2,
+                   "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 64}}}},
+    ],
+    "loop": {"start": 1, "stop": 3, "times": 2},
+}
+PRESETS["vofusun_2k"] = vofusun_sized(2048, 8, 16, 8192)
+PRESETS["vofusun_4k"] = vofusun_sized(4096, 8, 32, 14336)
 PRESETS["makisun_2k"] = makisun_sized(2048, 8, 16, 8192)
 PRESETS["makisun_4k"] = makisun_sized(4096, 8, 32, 14336)
 PRESETS["tebivik_2k"] = tebivik_sized(2048, 8, 16, 8192)

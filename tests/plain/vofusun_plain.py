@@ -141,18 +141,18 @@ def causal_conv_silu(x, w):
     return silu(y)
 
 
-def delta_mixer(h, P, p, m, eps):
-    """The gated delta rule, token by token: decay the state, correct what it says about k towards v, read it with q."""
-    T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = causal_conv_silu(h @ P[p + "q"].T, P[p + "q.conv"]).view(T, G, d)
-    k = causal_conv_silu(h @ P[p + "k"].T, P[p + "k.conv"]).view(T, G, d)
-    v = causal_conv_silu(h @ P[p + "v"].T, P[p + "v.conv"]).view(T, H, dv)
-    q = unit_vector(q) * d ** -0.5
-    k = unit_vector(k)
-    beta = torch.sigmoid(h @ P[p + "b"].T)  # [T, H]
+def decay_and_step(h, P, p):
+    """Per token and head: the state's decay g = exp(-exp(A_log) softplus(W_a h + dt_bias)) and the step beta = sigmoid(W_b h)."""
     decay = torch.exp(-torch.exp(P[p + "A_log"]) * torch.nn.functional.softplus(h @ P[p + "a"].T + P[p + "dt_bias"]))
-    S = torch.zeros(H, d, dv, dtype=F64)
+    return decay, torch.sigmoid(h @ P[p + "b"].T)
+
+
+def delta_recurrence(q, k, v, beta, decay, S=None):
+    """q, k [T, G, d]; v [T, H, dv]; beta, decay [T, H].  Token by token and head by head: decay the state, correct what
+    it says about k towards v by the step beta, then read it with q.  Returns o [T, H, dv] and the last state [H, d, dv]."""
+    T, G, d = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    S = torch.zeros(H, d, dv, dtype=F64) if S is None else S.clone()
     o = torch.zeros(T, H, dv, dtype=F64)
     for t in range(T):
         for a in range(H):
@@ -161,6 +161,20 @@ def delta_mixer(h, P, p, m, eps):
             u = beta[t, a] * (v[t, a] - S[a].T @ k[t, g])
             S[a] = S[a] + torch.outer(k[t, g], u)
             o[t, a] = S[a].T @ q[t, g]
+    return o, S
+
+
+def delta_mixer(h, P, p, m, eps):
+    """The gated delta rule behind short convolutions, with a normed and gated read-out."""
+    T = h.shape[0]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = causal_conv_silu(h @ P[p + "q"].T, P[p + "q.conv"]).view(T, G, d)
+    k = causal_conv_silu(h @ P[p + "k"].T, P[p + "k.conv"]).view(T, G, d)
+    v = causal_conv_silu(h @ P[p + "v"].T, P[p + "v.conv"]).view(T, H, dv)
+    q = unit_vector(q) * d ** -0.5
+    k = unit_vector(k)
+    decay, beta = decay_and_step(h, P, p)
+    o, _ = delta_recurrence(q, k, v, beta, decay)
     o = rms_divide(o, eps) * P[p + "norm"]
     o = o.reshape(T, H * dv) * silu(h @ P[p + "g"].T)
     return o @ P[p + "o"].T
