@@ -474,12 +474,15 @@ def run_compare(args) -> dict:
     weights, one GPU; with each model's device time by kernel for one prompt step and one decode step, and for the
     kernels that differ between the two the fraction of the measured roofline that they reach.
     --compare makisun: the same for Makisun beside Tebivik (the closest: recurrences and attention in turn, the same
-    norm kernels) at equal width, depth, head count and feed-forward size, and Makisun with routed experts."""
+    norm kernels) at equal width, depth, head count and feed-forward size, and Makisun with routed experts.
+    --compare vofusun: the same for Vofusun beside Makisun (the closest: windowed attention over the same pages and a
+    recurrence with a matrix state per head behind small per-token kernels) at equal width, depth, head count and
+    feed-forward size."""
     import torch
 
     import jax_llm_examples_b200 as J
     from jax_llm_examples_b200 import tracing
-    from jax_llm_examples_b200.config.presets import dense_llama_sized, makisun_sized, tebivik_sized
+    from jax_llm_examples_b200.config.presets import dense_llama_sized, makisun_sized, tebivik_sized, vofusun_sized
 
     peaks, peak_src = _peaks()
     hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
@@ -489,7 +492,8 @@ def run_compare(args) -> dict:
     sizes = [(2048, 8, 16, 8192), (4096, 8, 32, 14336)]
     if args.layers:
         sizes = [(w, args.layers, h, f) for w, _, h, f in sizes]
-    what = {"tebivik": "Tebivik beside a dense Llama-4-style decoder", "makisun": "Makisun beside Tebivik"}[args.compare]
+    what = {"tebivik": "Tebivik beside a dense Llama-4-style decoder", "makisun": "Makisun beside Tebivik",
+            "vofusun": "Vofusun beside Makisun"}[args.compare]
     out = {"metric": "prefill and decode throughput, " + what, "unit": "tok/s", "n_gpus": 1,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": peaks, "peaks_source": peak_src,
            "config": {"prefill_tokens": P, "decode_batch": B, "decode_context": C, "l2": "a 256 MiB buffer is written between timed steps"},
@@ -555,6 +559,49 @@ def run_compare(args) -> dict:
 
     clocks = ClockSampler()
     clocks.start()
+    for width, layers, heads, ff in sizes if args.compare == "vofusun" else ():
+        v, m = measure(vofusun_sized(width, layers, heads, ff)), measure(makisun_sized(width, layers, heads, ff))
+        # Vofusun's layers in turn: windowed attention, the delta rule, chunked attention; Makisun's: attention beside
+        # gated linear attention (half the heads), time mix
+        n_win, n_delta, n_chunk = (layers + 2) // 3, (layers + 1) // 3, layers // 3
+        par, rec = (layers + 1) // 2, layers // 2
+        dh, hkv, window, chunk = 128, max(heads // 4, 1), 1024, 2048
+        state = 128 * 128 * 8  # a head's state read and written, float32
+        m_heads = rec * heads + par * max(heads // 2, 1)
+        d_rows = (2 * max(heads // 2, 1) * 128 + 2 * heads * 128 + 2 * heads) * 4  # q, k (key heads), v in, o out, step and decay
+        m_rows = m_heads * 128 * 5 * 4
+        seen_w = sum(min(i + 1, window) for i in range(P))
+        seen_c = sum(i % chunk + 1 for i in range(P))
+        keys_w, keys_c = min(C, window), (C - 1) % chunk + 1  # keys a decoded token reads
+        vk = lambda d, k: d.get(k, 0)  # noqa: E731
+        roof = {
+            "decode": {
+                "vofusun delta_scan": frac(vk(v["decode_kernels_ms"], "jlx_delta_scan"), n_delta * B * (heads * state + d_rows)),
+                "makisun decay_scan": frac(vk(m["decode_kernels_ms"], "jlx_decay_scan"), B * (m_heads * state + m_rows)),
+                "vofusun attention_decode": frac(vk(v["decode_kernels_ms"], "jlx_attention_decode"),
+                                                 B * (n_win * keys_w + n_chunk * keys_c) * 2 * hkv * dh * 2),
+                "makisun attention_decode": frac(vk(m["decode_kernels_ms"], "jlx_attention_decode"), par * B * keys_w * 2 * hkv * dh * 2),
+                "vofusun add_rmsnorm": frac(vk(v["decode_kernels_ms"], "jlx_add_rmsnorm"), (2 * layers + 1) * B * width * 14),
+                "makisun group_norm": frac(vk(m["decode_kernels_ms"], "jlx_group_norm"), (2 * layers + 1) * B * width * 14),
+            },
+            "prefill": {
+                "vofusun delta_scan": frac(vk(v["prefill_kernels_ms"], "jlx_delta_scan"), n_delta * P * d_rows),
+                "makisun decay_scan": frac(vk(m["prefill_kernels_ms"], "jlx_decay_scan"), P * m_rows),
+                "vofusun attention_prefill_tc": frac(vk(v["prefill_kernels_ms"], "jlx_attention_prefill_tc"), 0,
+                                                     heads * (n_win * seen_w + n_chunk * seen_c) * 4 * dh),
+                "makisun attention_prefill_tc": frac(vk(m["prefill_kernels_ms"], "jlx_attention_prefill_tc"), 0, par * heads * seen_w * 4 * dh),
+                "vofusun add_rmsnorm": frac(vk(v["prefill_kernels_ms"], "jlx_add_rmsnorm"), (2 * layers + 1) * P * width * 14),
+                "makisun group_norm": frac(vk(m["prefill_kernels_ms"], "jlx_group_norm"), (2 * layers + 1) * P * width * 14),
+            },
+            # device time per token and head of the two recurrences (a chain of dependent steps: the figure that a
+            # prompt's time follows), ns
+            "scan_ns_per_token_and_layer": {
+                "vofusun delta_scan": round(vk(v["prefill_kernels_ms"], "jlx_delta_scan") * 1e6 / (P * max(n_delta, 1)), 1),
+                "makisun decay_scan": round(vk(m["prefill_kernels_ms"], "jlx_decay_scan") * 1e6 / (P * layers), 1),
+            },
+        }
+        out["sizes"].append({"width": width, "layers": layers, "heads": heads, "ff": ff, "vofusun": v, "makisun": m,
+                             "fraction_of_measured_roofline": roof})
     for width, layers, heads, ff in sizes if args.compare == "makisun" else ():
         m, t = measure(makisun_sized(width, layers, heads, ff)), measure(tebivik_sized(width, layers, heads, ff))
         routed = measure(makisun_sized(width, layers, heads, ff, experts=16))
@@ -638,7 +685,7 @@ def main() -> int:
     ap.add_argument("--long-tokens", type=int, default=32768)
     ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
-    ap.add_argument("--compare", default=None, choices=["tebivik", "makisun"],
+    ap.add_argument("--compare", default=None, choices=["tebivik", "makisun", "vofusun"],
                     help="instead of the benchmark: throughput of this architecture at real layer sizes beside the closest "
                     "model the framework had before (with --prefill-tokens, --batch, --context up to 4096, --layers)")
     args = ap.parse_args()

@@ -4,6 +4,7 @@
     python -m jax_llm_examples_b200.kernels.microbench attention_prefill --tokens 2048
     python -m jax_llm_examples_b200.kernels.microbench gemm --rows 8 --n 16384 --k 5120 [--experts 16] [--swiglu]
     python -m jax_llm_examples_b200.kernels.microbench decay_scan --tokens 2048 --requests 1 --heads 16 [--read-before]
+    python -m jax_llm_examples_b200.kernels.microbench delta_scan --tokens 2048 --requests 1 --heads 16 [--key-heads 8]
 
 The reference benchmarks its kernels the same way, from ``__main__`` blocks in the kernel files
 (llama4/llama4_jax/ragged_attention.py:299-418, llama4/llama4_jax/decode_ragged_dot.py:239-291).
@@ -153,6 +154,27 @@ def decay_scan(a) -> dict:
             "GFLOP/s": round(N * H * dk * dv * 5 / t / 1e9, 1)}
 
 
+def delta_scan(a) -> dict:
+    """The gated delta rule's recurrence: ``requests`` requests of ``tokens`` tokens each in one launch."""
+    dev = "cuda"
+    N, H, G, dk, dv = a.requests * a.tokens, a.heads, a.key_heads or a.heads, a.dim, a.vdim
+    q = torch.nn.functional.normalize(torch.randn(N, G, dk, device=dev), dim=-1) * dk ** -0.5
+    k, v = torch.nn.functional.normalize(torch.randn(N, G, dk, device=dev), dim=-1), torch.randn(N, H, dv, device=dev)
+    beta, decay = torch.rand(N, H, device=dev), torch.rand(N, H, device=dev) * 0.1 + 0.9
+    state, o = torch.zeros(a.requests, H, dk, dv, device=dev), torch.empty(N, H, dv, device=dev)
+    cu = (torch.arange(a.requests + 1, device=dev, dtype=torch.int32) * a.tokens).contiguous()
+    slots = torch.arange(a.requests, device=dev, dtype=torch.int32)
+
+    def run():
+        K.delta_scan(q, k, v, beta, decay, state, cu, slots, o)
+
+    t = _time(run, a.reps, _flush(a))
+    rows, states = N * (2 * G * dk + 2 * H * dv + 2 * H) * 4, a.requests * H * dk * dv * 8
+    return {"kernel": "delta_scan", "requests": a.requests, "tokens": a.tokens, "heads": H, "key_heads": G, "dim": dk, "vdim": dv,
+            "us": round(t * 1e6, 1), "ns_per_token": round(t * 1e9 / a.tokens, 1), "bytes": rows + states,
+            "GB/s": round((rows + states) / t / 1e9, 1), "GFLOP/s": round(N * H * dk * dv * 7 / t / 1e9, 1)}
+
+
 def _flush(a):
     return None if a.no_flush else torch.empty(256 * 1024 * 1024 // 4, device="cuda")
 
@@ -160,16 +182,19 @@ def _flush(a):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan"):
+    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan", "delta_scan"):
         p = sub.add_parser(name)
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
-        if name == "decay_scan":
+        if name == "delta_scan":
+            p.add_argument("--key-heads", type=int, default=0, help="heads of q and k (0: as many as value heads)")
+        if name in ("decay_scan", "delta_scan"):
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--requests", type=int, default=1)
             p.add_argument("--heads", type=int, default=16)
             p.add_argument("--dim", type=int, default=128)
             p.add_argument("--vdim", type=int, default=128)
+        if name == "decay_scan":
             p.add_argument("--read-before", action="store_true", help="o from the state before the update, with a bonus (time mixing)")
         if name.startswith("attention"):
             p.add_argument("--heads", type=int, default=40)
@@ -193,7 +218,8 @@ def main(argv=None) -> int:
             p.add_argument("--hint", type=int, default=0, help="rows per group that the token tile is sized for (0: twice the mean)")
             p.add_argument("--swiglu", action="store_true", help="fused SiLU(gate) * up epilogue")
     a = ap.parse_args(argv)
-    print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "decay_scan": decay_scan}[a.what](a)))
+    print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "decay_scan": decay_scan,
+                      "delta_scan": delta_scan}[a.what](a)))
     return 0
 
 
