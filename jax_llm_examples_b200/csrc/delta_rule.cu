@@ -167,134 +167,304 @@ JLX_API int jlx_conv_unit_prep(const RowsView* proj, int b_col, int a_col, const
 }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
-// One block per (request, head, slice of COLS value columns).  A column of S belongs to four neighbouring lanes, each
-// keeping RPT of its rows in registers (row i = part * RPT + r; rows from dk on hold zeros and stay zero), so the two
-// sums over a column's rows are RPT products per lane and two shuffles; no barrier stands between two tokens.  Both
-// sums are taken over the state as the token found it:
+// One block of DELTA_W warps per (request, head, slice of 32 value columns).  Lane = a value column; warp w keeps rows
+// [w NR, (w+1) NR) of S for that column in registers (rows from dk on hold zeros and stay zero), so a key's or query's
+// rows are read from shared memory at one address by the whole warp.
 //
-//     a = k . S[:, j],  b = q . S[:, j];   u = beta (v_j - g a);   S[:, j] <- g S[:, j] + k u;   o_j = g b + (q . k) u,
+// Walking token by token, every token waits for its predecessor's write (S^T k needs the state just written): one
+// long chain of dependent sums per token.  The kernel walks DELTA_TB tokens at a time instead.  With c_t = g_0 ... g_t
+// (decays of the group), the state S0 the group found, and column j:
 //
-// which is the rule above with the read-out written through the update (o = (g S + k u^T)^T q), so that a token costs
-// one round of shuffles.  The tokens' q and k rows, v slice, beta, g and q . k come through shared memory SCAN_TB
-// tokens at a time.  A token's arithmetic is the same wherever it stands in a step.
-#define SCAN_TB 16
-#define DELTA_COLS 32  // value columns per block: 128 threads
+//     P_t = k_t . S0[:, j],   B_t = q_t . S0[:, j]                                   (no token waits for another)
+//     a_t = c_t P_t + sum_{s<t}  (c_t / c_s) (k_s . k_t) u_s,    u_t = beta_t (v_tj - a_t)
+//     o_tj = c_t B_t + sum_{s<=t} (c_t / c_s) (k_s . q_t) u_s                        (scalars only: a short chain)
+//     S[:, j] <- c_last S0[:, j] + sum_t (c_last / c_t) k_t u_t                      (no token waits for another)
+//
+// which is the rule above with the sums taken in another order; nothing is inverted and nothing leaves 32-bit.  The
+// ratios c_t / c_s are running products of decays, never quotients: (c_t / c_s) u_s is kept per write and decays with
+// every later token, and is what the state gets at the group's end.  The warps' parts of P and B meet in shared
+// memory once per group (warp w adds token w's); every warp then walks the scalars (it needs all u for its rows),
+// and token t's o is made by warp t.  The products k_s . k_t and k_s . q_t do not depend on the column or on the value head: delta_gram
+// makes them once per token and key head for steps that hold prompts; with single tokens only, a block makes its own
+// (one product).  Rows, v slice, beta, g and the products come through shared memory, two buffers taking turns:
+// while a group is walked, asynchronous copies bring the next.  Groups count from a request's first token of the
+// step, so the order of a token's sums, and with it the last bits of its result, depends on where the step begins;
+// nothing else in the batch enters.
+#define DELTA_TB 8
+#define DELTA_W 8  // warps of a scan block: as many as tokens in a group
 
-template <int RPT>
-__global__ void __launch_bounds__(128) delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k,
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// gram [N, G, 2, DELTA_TB]: for token n, the t-th of its group (groups count from its request's first token of the
+// step), [0][s] = k_(n-t+s) . q_n for s <= t and [1][s] = k_(n-t+s) . k_n for s < t.  The rest is never read.
+// One warp per (token, key head).
+__global__ void __launch_bounds__(256) delta_gram_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                         const int* __restrict__ cu_q, const int* __restrict__ req_of_token,
+                                                         float* __restrict__ gram, int G, int dk) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int n = blockIdx.x, lane = threadIdx.x & 31;
+  const int t = (n - cu_q[req_of_token[n]]) % DELTA_TB;
+  for (int kh = threadIdx.x >> 5; kh < G; kh += blockDim.x >> 5) {
+    const float* qn = q + ((size_t)n * G + kh) * dk;
+    const float* kn = k + ((size_t)n * G + kh) * dk;
+    float* out = gram + ((size_t)n * G + kh) * 2 * DELTA_TB;
+    for (int s = 0; s <= t; ++s) {
+      const float* y = k + ((size_t)(n - t + s) * G + kh) * dk;
+      float dq = 0.f, dkk = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        dq = fmaf(qn[i], y[i], dq);
+        dkk = fmaf(kn[i], y[i], dkk);
+      }
+      dq = warp_sum(dq);
+      dkk = warp_sum(dkk);
+      if (lane == 0) {
+        out[s] = dq;
+        out[DELTA_TB + s] = dkk;
+      }
+    }
+  }
+}
+
+template <int NR>
+__global__ void __launch_bounds__(DELTA_W * 32) delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k,
                                                          const float* __restrict__ v, const float* __restrict__ beta,
                                                          const float* __restrict__ decay, float* __restrict__ state,
                                                          const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
-                                                         float* __restrict__ o, int G, int H, int dk, int dv) {
+                                                         const float* __restrict__ gram, float* __restrict__ o, int G, int H,
+                                                         int dk, int dv) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
-  constexpr int LDP = RPT + 4;       // a part's rows in shared memory, padded so that the four parts fall into other banks
-  constexpr int ROW = 4 * LDP;
-  __shared__ __align__(16) float qs[SCAN_TB][ROW], ks[SCAN_TB][ROW];
-  __shared__ float vs[SCAN_TB][DELTA_COLS], bs[SCAN_TB], gs[SCAN_TB], qk[SCAN_TB];
-  const int r = blockIdx.z, hd = blockIdx.y, j0 = blockIdx.x * DELTA_COLS;
+  constexpr int T = DELTA_TB;
+  constexpr int W = DELTA_W;
+  static_assert(T % 4 == 0 && NR % 4 == 0 && W == T, "rows and products are read four at a time; a warp per token of a group");
+  extern __shared__ __align__(16) float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int dkp = W * NR;
+  constexpr int stage_floats = 2 * T * dkp + T * 32 + 2 * T + 2 * T * T;  // q rows | k rows | v slice | beta | g | k.q | k.k
+  float* parts = smem + 2 * stage_floats;                                   // [2][T][W][32]: the warps' parts of P and B
+  float* sums = parts + 2 * T * W * 32;                                     // [2][T][32]: P and B
+  const int r = blockIdx.z, hd = blockIdx.y, j0 = blockIdx.x * 32;
   const int kh = hd / (H / G);
-  const int part = threadIdx.x & 3, col = threadIdx.x >> 2;
-  const int j = j0 + col;
+  const int j = j0 + lane;
   const bool col_ok = j < dv;
+  const int i0 = warp * NR;
+  for (int idx = threadIdx.x; idx < 2 * stage_floats; idx += blockDim.x) smem[idx] = 0.f;  // rows beyond dk, columns beyond dv
+  __syncthreads();
   pdl_wait();
   const int n0 = cu_q[r], n1 = cu_q[r + 1];
   if (n1 <= n0) return;
   float* S = state + ((size_t)slot_ids[r] * H + hd) * dk * dv;
-  float s[RPT];
+  float s[NR];
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int row = part * RPT + i;
-    s[i] = (col_ok && row < dk) ? S[(size_t)row * dv + j] : 0.f;
-  }
-  for (int t0 = n0; t0 < n1; t0 += SCAN_TB) {
-    const int cnt = min(SCAN_TB, n1 - t0);
-    __syncthreads();  // the previous group is walked
-    for (int idx = threadIdx.x; idx < cnt * 4 * RPT; idx += 128) {
-      const int t = idx / (4 * RPT), e = idx - t * 4 * RPT;  // e = the row
-      const int at = (e / RPT) * LDP + e % RPT;
-      const size_t src = ((size_t)(t0 + t) * G + kh) * dk + e;
-      qs[t][at] = e < dk ? q[src] : 0.f;
-      ks[t][at] = e < dk ? k[src] : 0.f;
+  for (int i = 0; i < NR; ++i) s[i] = (col_ok && i0 + i < dk) ? S[(size_t)(i0 + i) * dv + j] : 0.f;
+  const bool vec = (dk & 3) == 0 && (dv & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0);
+  const int nv = min(32, dv - j0);
+  auto stage = [&](int t0, int b) {  // asynchronous copies of a group's rows into buffer b
+    float* st = smem + b * stage_floats;
+    const int cnt = min(T, n1 - t0);
+    if (vec) {
+      const int dk4 = dk >> 2, nv4 = nv >> 2;
+      for (int idx = threadIdx.x; idx < cnt * dk4; idx += blockDim.x) {
+        const int tt = idx / dk4, e = (idx - tt * dk4) << 2;
+        const size_t src = ((size_t)(t0 + tt) * G + kh) * dk + e;
+        cp_async16(st + tt * dkp + e, q + src);
+        cp_async16(st + T * dkp + tt * dkp + e, k + src);
+      }
+      for (int idx = threadIdx.x; idx < cnt * nv4; idx += blockDim.x) {
+        const int tt = idx / nv4, l = (idx - tt * nv4) << 2;
+        cp_async16(st + 2 * T * dkp + tt * 32 + l, v + ((size_t)(t0 + tt) * H + hd) * dv + j0 + l);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < cnt * dk; idx += blockDim.x) {
+        const int tt = idx / dk, e = idx - tt * dk;
+        const size_t src = ((size_t)(t0 + tt) * G + kh) * dk + e;
+        cp_async4(st + tt * dkp + e, q + src);
+        cp_async4(st + T * dkp + tt * dkp + e, k + src);
+      }
+      for (int idx = threadIdx.x; idx < cnt * nv; idx += blockDim.x) {
+        const int tt = idx / nv, l = idx - tt * nv;
+        cp_async4(st + 2 * T * dkp + tt * 32 + l, v + ((size_t)(t0 + tt) * H + hd) * dv + j0 + l);
+      }
     }
-    for (int idx = threadIdx.x; idx < cnt * DELTA_COLS; idx += 128) {
-      const int t = idx / DELTA_COLS, c = idx - t * DELTA_COLS;
-      vs[t][c] = j0 + c < dv ? v[((size_t)(t0 + t) * H + hd) * dv + j0 + c] : 0.f;
+    float* small = st + 2 * T * dkp + T * 32;
+    for (int idx = threadIdx.x; idx < cnt; idx += blockDim.x) {
+      cp_async4(small + idx, beta + (size_t)(t0 + idx) * H + hd);
+      cp_async4(small + T + idx, decay + (size_t)(t0 + idx) * H + hd);
     }
-    if ((int)threadIdx.x < cnt) {
-      bs[threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * H + hd];
-      gs[threadIdx.x] = decay[(size_t)(t0 + threadIdx.x) * H + hd];
-    }
-    __syncthreads();
-    // q . k of every token of the group: eight threads per token, rows in a fixed order (the padding between the
-    // parts is never written, so the product walks rows, not entries)
-    {
-      const int t = threadIdx.x >> 3, sub = threadIdx.x & 7;
-      float d = 0.f;
-      if (t < cnt)
-        for (int e = sub; e < 4 * RPT; e += 8) {
-          const int at = (e / RPT) * LDP + e % RPT;
-          d = fmaf(qs[t][at], ks[t][at], d);
+    if (gram)  // a token's 2 T products are 16-byte aligned rows
+      for (int idx = threadIdx.x; idx < cnt * (2 * T / 4); idx += blockDim.x) {
+        const int tt = idx / (2 * T / 4), part = idx - tt * (2 * T / 4);  // part: T / 4 pieces of k.q, then of k.k
+        const int which = part / (T / 4), piece = part - which * (T / 4);
+        cp_async16(small + 2 * T + which * T * T + tt * T + piece * 4,
+                   gram + (((size_t)(t0 + tt) * G + kh) * 2 + which) * T + piece * 4);
+      }
+    cp_async_commit();
+  };
+
+  stage(n0, 0);
+  int b = 0;
+  for (int t0 = n0; t0 < n1; t0 += T, b ^= 1) {
+    const int cnt = min(T, n1 - t0);
+    cp_async_wait_all();
+    __syncthreads();  // this group's rows are there; the group before is walked: its buffer and the parts are free
+    if (t0 + T < n1) stage(t0 + T, b ^ 1);
+    float* st = smem + b * stage_floats;
+    const float* qs = st;
+    const float* ks = qs + T * dkp;
+    const float* vs = ks + T * dkp;
+    const float* bs = vs + T * 32;
+    const float* gs = bs + T;
+    float* Mqk = st + 2 * T * dkp + T * 32 + 2 * T;  // [T][T], s <= t: k_s . q_t
+    float* Mkk = Mqk + T * T;                         // [T][T], s < t:  k_s . k_t
+    if (!gram)  // two threads per product, whole warps per round: every lane takes part in the shuffle
+      for (int id = threadIdx.x; id < 2 * T * T; id += blockDim.x) {
+        int gt = 0, gsrc = id >> 1;  // T (T + 1) / 2 products k_s . q_t, then T (T - 1) / 2 products k_s . k_t
+        const bool g_qk = gsrc < T * (T + 1) / 2;
+        if (g_qk) {
+          while (gsrc > gt) gsrc -= ++gt;
+        } else {
+          gsrc -= T * (T + 1) / 2;
+          gt = 1;
+          while (gsrc >= gt) gsrc -= gt++;
         }
-      d += __shfl_xor_sync(0xffffffffu, d, 1);
-      d += __shfl_xor_sync(0xffffffffu, d, 2);
-      d += __shfl_xor_sync(0xffffffffu, d, 4);
-      if (t < cnt && sub == 0) qk[t] = d;
-    }
-    __syncthreads();
-    for (int t = 0; t < cnt; ++t) {
-      const float* kp = &ks[t][part * LDP];
-      const float* qp = &qs[t][part * LDP];
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-#pragma unroll
-      for (int i = 0; i < RPT; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
-        const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
-        a0 = fmaf(k4.x, s[i], a0); a1 = fmaf(k4.y, s[i + 1], a1); a0 = fmaf(k4.z, s[i + 2], a0); a1 = fmaf(k4.w, s[i + 3], a1);
-        b0 = fmaf(q4.x, s[i], b0); b1 = fmaf(q4.y, s[i + 1], b1); b0 = fmaf(q4.z, s[i + 2], b0); b1 = fmaf(q4.w, s[i + 3], b1);
+        float d = 0.f;
+        if (gt < cnt) {
+          const float* x = (g_qk ? qs : ks) + gt * dkp;
+          const float* y = ks + gsrc * dkp;
+          for (int e = (id & 1) * 4; e < dkp; e += 8) {
+            const float4 x4 = *reinterpret_cast<const float4*>(x + e);
+            const float4 y4 = *reinterpret_cast<const float4*>(y + e);
+            d = fmaf(x4.x, y4.x, d); d = fmaf(x4.y, y4.y, d); d = fmaf(x4.z, y4.z, d); d = fmaf(x4.w, y4.w, d);
+          }
+        }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        if (gt < cnt && (id & 1) == 0) (g_qk ? Mqk : Mkk)[gt * T + gsrc] = d;
       }
-      float a = a0 + a1, b = b0 + b1;
-      a += __shfl_xor_sync(0xffffffffu, a, 1);
-      b += __shfl_xor_sync(0xffffffffu, b, 1);
-      a += __shfl_xor_sync(0xffffffffu, a, 2);
-      b += __shfl_xor_sync(0xffffffffu, b, 2);
-      const float g = gs[t];
-      const float u = bs[t] * (vs[t][col] - g * a);
+    // the warp's part of the sums over the state as the group found it
 #pragma unroll
-      for (int i = 0; i < RPT; i += 4) {  // the key's rows once more from shared memory: cheaper than RPT registers
-        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
-        s[i] = fmaf(k4.x, u, g * s[i]); s[i + 1] = fmaf(k4.y, u, g * s[i + 1]);
-        s[i + 2] = fmaf(k4.z, u, g * s[i + 2]); s[i + 3] = fmaf(k4.w, u, g * s[i + 3]);
+    for (int t = 0; t < T; ++t)
+      if (t < cnt) {
+        const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
+        const float4* qp = reinterpret_cast<const float4*>(qs + t * dkp + i0);
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; i += 4) {
+          const float4 k4 = kp[i >> 2], q4 = qp[i >> 2];
+          a0 = fmaf(k4.x, s[i], a0); a1 = fmaf(k4.y, s[i + 1], a1); a0 = fmaf(k4.z, s[i + 2], a0); a1 = fmaf(k4.w, s[i + 3], a1);
+          b0 = fmaf(q4.x, s[i], b0); b1 = fmaf(q4.y, s[i + 1], b1); b0 = fmaf(q4.z, s[i + 2], b0); b1 = fmaf(q4.w, s[i + 3], b1);
+        }
+        parts[(t * W + warp) * 32 + lane] = a0 + a1;
+        parts[((T + t) * W + warp) * 32 + lane] = b0 + b1;
       }
-      if (part == 0 && col_ok) o[((size_t)(t0 + t) * H + hd) * dv + j] = fmaf(qk[t], u, g * b);
+    __syncthreads();  // the parts are there
+    if (warp < cnt) {  // this warp adds the parts of token `warp`
+      float Pt = 0.f, Bt = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) {
+        Pt += parts[(warp * W + w) * 32 + lane];
+        Bt += parts[((T + warp) * W + w) * 32 + lane];
+      }
+      sums[warp * 32 + lane] = Pt;
+      sums[(T + warp) * 32 + lane] = Bt;
     }
+    __syncthreads();  // P, B and the products are there
+    // the writes, one after another: scalars of this column only.  ud[x] = (c_t / c_x) u_x as token t sees it.
+    float ud[T];
+    float c = 1.f;
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      ud[t] = 0.f;
+      if (t < cnt) {
+        float mk[T], mq[T];
+#pragma unroll
+        for (int s4 = 0; s4 < T; s4 += 4) {
+          if (s4 < t) *reinterpret_cast<float4*>(mk + s4) = *reinterpret_cast<const float4*>(Mkk + t * T + s4);
+          if (s4 <= t) *reinterpret_cast<float4*>(mq + s4) = *reinterpret_cast<const float4*>(Mqk + t * T + s4);
+        }
+        const float g = gs[t];
+        c *= g;
+        float a = c * sums[t * 32 + lane];
+#pragma unroll
+        for (int x = 0; x < t; ++x) {
+          ud[x] *= g;
+          a = fmaf(mk[x], ud[x], a);
+        }
+        ud[t] = bs[t] * (vs[t * 32 + lane] - a);
+        if (t == warp) {  // this warp makes the token's o
+          float ov = c * sums[(T + t) * 32 + lane];
+#pragma unroll
+          for (int x = 0; x <= t; ++x) ov = fmaf(mq[x], ud[x], ov);
+          if (col_ok) o[((size_t)(t0 + t) * H + hd) * dv + j] = ov;
+        }
+      }
+    }
+    // the state after the group: c = the group's whole decay, ud = every write decayed by the tokens after it
+#pragma unroll
+    for (int i = 0; i < NR; ++i) s[i] *= c;
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+      if (t < cnt) {
+        const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
+#pragma unroll
+        for (int i = 0; i < NR; i += 4) {
+          const float4 k4 = kp[i >> 2];
+          s[i] = fmaf(k4.x, ud[t], s[i]); s[i + 1] = fmaf(k4.y, ud[t], s[i + 1]);
+          s[i + 2] = fmaf(k4.z, ud[t], s[i + 2]); s[i + 3] = fmaf(k4.w, ud[t], s[i + 3]);
+        }
+      }
   }
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int row = part * RPT + i;
-    if (col_ok && row < dk) S[(size_t)row * dv + j] = s[i];
-  }
+  for (int i = 0; i < NR; ++i)
+    if (col_ok && i0 + i < dk) S[(size_t)(i0 + i) * dv + j] = s[i];
 }
 
-// q, k: float32 [N, G, dk]; v, o: [N, H, dv]; beta, decay: [N, H]; state: float32 [slots, H, dk, dv].
-JLX_API int jlx_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay, float* state,
-                           const int* cu_q, const int* slot_ids, float* o, int R, int G, int H, int dk, int dv, cudaStream_t stream) {
-  JLX_REQUIRE(R >= 0 && G > 0 && H > 0 && dk > 0 && dv > 0 && H % G == 0, "delta_scan: bad sizes R=%d G=%d H=%d dk=%d dv=%d", R, G, H, dk, dv);
-  JLX_REQUIRE(dk <= 256, "delta_scan: key size %d is above the supported maximum 256", dk);
-  JLX_REQUIRE(H <= 65535 && R <= 65535, "delta_scan: too many heads or requests");
-  if (R == 0) return 0;
-  const dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, H, R);
-  const int rpt = (dk + 3) / 4;
-#define DELTA_LAUNCH(RPT)                                                                                                \
-  JLX_CUDA(jlx_launch_pdl(delta_scan_kernel<RPT>, grid, dim3(128), 0, stream, q, k, v, beta, decay, state, cu_q, slot_ids, o, G, H, dk, dv))
-  if (rpt <= 4) DELTA_LAUNCH(4);
-  else if (rpt <= 8) DELTA_LAUNCH(8);
-  else if (rpt <= 16) DELTA_LAUNCH(16);
-  else if (rpt <= 24) DELTA_LAUNCH(24);
-  else if (rpt <= 32) DELTA_LAUNCH(32);
-  else if (rpt <= 48) DELTA_LAUNCH(48);
-  else DELTA_LAUNCH(64);
-#undef DELTA_LAUNCH
+template <int NR>
+static int launch_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay, float* state,
+                             const int* cu_q, const int* slot_ids, const float* gram, float* o, int R, int G, int H, int dk, int dv,
+                             cudaStream_t stream) {
+  constexpr int W = DELTA_W;
+  constexpr size_t smem = sizeof(float) * (2 * ((size_t)2 * DELTA_TB * W * NR + DELTA_TB * 32 + 2 * DELTA_TB + 2 * DELTA_TB * DELTA_TB) +
+                                           (size_t)2 * DELTA_TB * W * 32 + 2 * DELTA_TB * 32);
+  if (smem > 48 * 1024) JLX_CUDA(cudaFuncSetAttribute(delta_scan_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  JLX_CUDA(jlx_launch_pdl(delta_scan_kernel<NR>, dim3((dv + 31) / 32, H, R), dim3(W * 32), smem, stream, q, k, v, beta, decay, state, cu_q,
+                          slot_ids, gram, o, G, H, dk, dv));
   JLX_LAUNCH_CHECK("delta_scan");
   return 0;
+}
+
+// q, k: float32 [N, G, dk]; v, o: [N, H, dv]; beta, decay: [N, H]; state: float32 [slots, H, dk, dv]; gram: scratch
+// float32 [N, G, 2, DELTA_TB] on a 16-byte boundary, or null (every block then makes the products of its groups itself).
+JLX_API int jlx_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay, float* state,
+                           const int* cu_q, const int* slot_ids, const int* req_of_token, float* gram, float* o, int N, int R, int G,
+                           int H, int dk, int dv, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && R >= 0 && G > 0 && H > 0 && dk > 0 && dv > 0 && H % G == 0, "delta_scan: bad sizes N=%d R=%d G=%d H=%d dk=%d dv=%d", N,
+              R, G, H, dk, dv);
+  JLX_REQUIRE(dk <= 256, "delta_scan: key size %d is above the supported maximum 256", dk);
+  JLX_REQUIRE(H <= 65535 && R <= 65535, "delta_scan: too many heads or requests");
+  JLX_REQUIRE(!gram || (req_of_token && ((uintptr_t)gram & 15) == 0), "delta_scan: the products' scratch needs a 16-byte boundary and the tokens' requests");
+  if (R == 0 || N == 0) return 0;
+  if (N <= R) gram = nullptr;  // single tokens: one product per block, not worth a launch
+  if (gram) {
+    const int warps = G < 8 ? G : 8;
+    JLX_CUDA(jlx_launch_pdl(delta_gram_kernel, dim3(N), dim3(warps * 32), 0, stream, q, k, cu_q, req_of_token, gram, G, dk));
+    JLX_LAUNCH_CHECK("delta_gram");
+  }
+#define DELTA_ARGS q, k, v, beta, decay, state, cu_q, slot_ids, gram, o, R, G, H, dk, dv, stream
+  const int nr = (dk + DELTA_W - 1) / DELTA_W;  // rows per warp
+  if (nr <= 4) return launch_delta_scan<4>(DELTA_ARGS);
+  if (nr <= 8) return launch_delta_scan<8>(DELTA_ARGS);
+  if (nr <= 12) return launch_delta_scan<12>(DELTA_ARGS);
+  if (nr <= 16) return launch_delta_scan<16>(DELTA_ARGS);
+  if (nr <= 24) return launch_delta_scan<24>(DELTA_ARGS);
+  return launch_delta_scan<32>(DELTA_ARGS);
+#undef DELTA_ARGS
 }

@@ -543,11 +543,16 @@ def conv_unit_prep(proj: _RowsView, b_col: int, a_col: int, conv_w: torch.Tensor
          c_int(taps), c_int(CONV_ACTIVATIONS[activation]), c_float(unit_eps), c_float(q_scale), _stream())
 
 
+DELTA_GROUP = 8  # tokens that delta_scan walks together (csrc/delta_rule.cu)
+
+
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
-               cu_q: torch.Tensor, slot_ids: torch.Tensor, o: torch.Tensor) -> None:
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, o: torch.Tensor, req_of_token: torch.Tensor | None = None,
+               scratch: torch.Tensor | None = None) -> None:
     """Over each request's tokens, in order:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
     q, k: float32 [N, G, dk] (head h reads key head h // (H / G)); v, o: [N, H, dv]; beta, decay: [N, H];
-    state: float32 [slots, H, dk, dv]."""
+    state: float32 [slots, H, dk, dv].  With `req_of_token` [N] and `scratch` (float32, N * G * 2 * DELTA_GROUP elements) a
+    step that holds prompts makes the products between a group's keys and queries once per key head, ahead of the scan."""
     _contig(q, k, v, beta, decay, state, o)
     N, G, dk = q.shape
     _, H, dv = v.shape
@@ -555,8 +560,12 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
         raise KernelError("delta_scan: everything is float32")
     if tuple(state.shape[1:]) != (H, dk, dv) or tuple(o.shape) != (N, H, dv) or tuple(k.shape) != (N, G, dk) or H % G:
         raise KernelError(f"delta_scan: shapes do not fit: q {tuple(q.shape)}, v {tuple(v.shape)}, state {tuple(state.shape)}")
+    ahead = req_of_token is not None and scratch is not None
+    if ahead and (scratch.dtype != torch.float32 or scratch.numel() < N * G * 2 * DELTA_GROUP or not scratch.is_contiguous()):
+        raise KernelError(f"delta_scan: the scratch holds {scratch.numel()} elements; {N * G * 2 * DELTA_GROUP} float32 are needed")
     _run("delta_rule", "jlx_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(cu_q), _ptr(slot_ids),
-         _ptr(o), c_int(slot_ids.numel()), c_int(G), c_int(H), c_int(dk), c_int(dv), _stream())
+         _ptr(req_of_token) if ahead else None, _ptr(scratch) if ahead else None, _ptr(o), c_int(N), c_int(slot_ids.numel()), c_int(G),
+         c_int(H), c_int(dk), c_int(dv), _stream())
 
 
 # ---------------------------------- weighted q/k norm + rotate-half rotation + page write; gated attention heads

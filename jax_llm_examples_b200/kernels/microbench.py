@@ -164,9 +164,11 @@ def delta_scan(a) -> dict:
     state, o = torch.zeros(a.requests, H, dk, dv, device=dev), torch.empty(N, H, dv, device=dev)
     cu = (torch.arange(a.requests + 1, device=dev, dtype=torch.int32) * a.tokens).contiguous()
     slots = torch.arange(a.requests, device=dev, dtype=torch.int32)
+    req = torch.arange(a.requests, device=dev, dtype=torch.int32).repeat_interleave(a.tokens).contiguous()
+    scratch = None if a.products_in_block else torch.empty(N * G * 2 * K.DELTA_GROUP, device=dev)
 
     def run():
-        K.delta_scan(q, k, v, beta, decay, state, cu, slots, o)
+        K.delta_scan(q, k, v, beta, decay, state, cu, slots, o, req, scratch)
 
     t = _time(run, a.reps, _flush(a))
     rows, states = N * (2 * G * dk + 2 * H * dv + 2 * H) * 4, a.requests * H * dk * dv * 8
@@ -188,6 +190,7 @@ def main(argv=None) -> int:
         p.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
         if name == "delta_scan":
             p.add_argument("--key-heads", type=int, default=0, help="heads of q and k (0: as many as value heads)")
+            p.add_argument("--products-in-block", action="store_true", help="no launch ahead for the products between a group's keys and queries")
         if name in ("decay_scan", "delta_scan"):
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--requests", type=int, default=1)

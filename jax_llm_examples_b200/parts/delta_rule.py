@@ -62,7 +62,7 @@ class GatedDeltaRule(ProjectedMixer):
         H, G, dk, dv, C = self.heads, self.key_heads, self.dim, self.vdim, self.channels
         conv_state, S = (cache.states[0], cache.states[1]) if self.taps > 1 else (None, cache.states[0])
         n, dev = proj.data.shape[-2], out.device
-        need = n * (2 * G * dk + 2 * H * dv + 2 * H)
+        need = n * (2 * G * K.DELTA_GROUP + 2 * G * dk + 2 * H * dv + 2 * H)
         buf = ctx.workspace.get("delta_rule", need, torch.float32) if ctx.workspace is not None else \
             torch.empty(need, dtype=torch.float32, device=dev)
         at = 0
@@ -76,6 +76,7 @@ class GatedDeltaRule(ProjectedMixer):
             at += size
             return t
 
+        products = cut(n, G, 2 * K.DELTA_GROUP)  # first: it is copied 16 bytes at a time
         q, k, v, o = cut(n, G, dk), cut(n, G, dk), cut(n, H, dv), cut(n, H, dv)
         beta, decay = cut(n, H), cut(n, H)
         gate_col = col + C
@@ -83,7 +84,7 @@ class GatedDeltaRule(ProjectedMixer):
             K.conv_unit_prep(K.rows_view(proj.data, proj.splits, col), C + H * dv, C + H * dv + H, self.conv_weight, conv_state,
                              self.rate_log, self.a_bias, ctx.cu_q, ctx.q_start, ctx.slot_ids, ctx.req_of_token, ctx.positions,
                              q, k, v, beta, decay, self.activation, self.unit_eps, self.q_scale)
-            K.delta_scan(q, k, v, beta, decay, S, ctx.cu_q, ctx.slot_ids, o)
+            K.delta_scan(q, k, v, beta, decay, S, ctx.cu_q, ctx.slot_ids, o, ctx.req_of_token, products)
             K.head_norm_gate(o, self.norm_weight, False, K.rows_view(proj.data, proj.splits, gate_col), self.eps, mult, out)
 
 

@@ -118,16 +118,18 @@ def row_err(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.sqrt((d ** 2).mean()) / max(np.sqrt(((ref - ref.mean()) ** 2).mean()), 1e-9))
 
 
-def compare(folder, requests: dict, got: dict, dtype: str) -> float:
-    """Every logit row a trace produced against the plain implementation's row at that place."""
+def compare(folder, requests: dict, got: dict, dtype: str, stray: int = 0) -> float:
+    """Every logit row a trace produced against the plain implementation's row at that place.  Among hundreds of rows
+    `stray` of them may scatter past the cap for a single row, up to twice as far; the mean stays as tight."""
     errs = []
     for rid, toks in requests.items():
         ref = plain_logits(folder, toks)
         for pos in range(len(toks)):
             if (rid, pos) in got:
                 err = row_err(got[(rid, pos)], ref[pos])
-                assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
+                assert err < TOL[dtype] * (2 if stray else 1), f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
                 errs.append(err)
+    assert sum(e >= TOL[dtype] for e in errs) <= stray, f"{dtype}: more than {stray} rows beyond {TOL[dtype]}"
     mean = float(np.mean(errs))
     assert mean < TOL_MEAN[dtype], f"{dtype}: mean relative error {mean:.3e} over {len(errs)} rows"
     return max(errs)
