@@ -15,6 +15,8 @@
 //
 // Every sum runs in an order that depends on the token alone, so a token's result does not change with the batch or
 // with how its prompt was cut into steps.
+#include <type_traits>
+
 #include "common.cuh"
 
 // Projected rows that may still be split-K partials: element (row, col) = sum_z p[z * split_stride + row * ld + col].
@@ -257,8 +259,10 @@ __global__ void __launch_bounds__(DELTA_W * 32) delta_scan_kernel(const float* _
   const int j = j0 + lane;
   const bool col_ok = j < dv;
   const int i0 = warp * NR;
-  for (int idx = threadIdx.x; idx < 2 * stage_floats; idx += blockDim.x) smem[idx] = 0.f;  // rows beyond dk, columns beyond dv
-  __syncthreads();
+  if (dk < dkp || dv - j0 < 32) {  // what no copy ever writes: rows beyond dk, columns beyond dv
+    for (int idx = threadIdx.x; idx < 2 * stage_floats; idx += blockDim.x) smem[idx] = 0.f;
+    __syncthreads();
+  }
   pdl_wait();
   const int n0 = cu_q[r], n1 = cu_q[r + 1];
   if (n1 <= n0) return;
@@ -349,78 +353,84 @@ __global__ void __launch_bounds__(DELTA_W * 32) delta_scan_kernel(const float* _
         d += __shfl_xor_sync(0xffffffffu, d, 1);
         if (gt < cnt && (id & 1) == 0) (g_qk ? Mqk : Mkk)[gt * T + gsrc] = d;
       }
-    // the warp's part of the sums over the state as the group found it
+    // A whole group is walked by code without a test per token, so that the tokens' loads and sums overlap.
+    auto walk = [&](auto whole) {
+      constexpr bool WHOLE = decltype(whole)::value;
+      // the warp's part of the sums over the state as the group found it
 #pragma unroll
-    for (int t = 0; t < T; ++t)
-      if (t < cnt) {
-        const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
-        const float4* qp = reinterpret_cast<const float4*>(qs + t * dkp + i0);
-        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+      for (int t = 0; t < T; ++t)
+        if (WHOLE || t < cnt) {
+          const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
+          const float4* qp = reinterpret_cast<const float4*>(qs + t * dkp + i0);
+          float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < NR; i += 4) {
-          const float4 k4 = kp[i >> 2], q4 = qp[i >> 2];
-          a0 = fmaf(k4.x, s[i], a0); a1 = fmaf(k4.y, s[i + 1], a1); a0 = fmaf(k4.z, s[i + 2], a0); a1 = fmaf(k4.w, s[i + 3], a1);
-          b0 = fmaf(q4.x, s[i], b0); b1 = fmaf(q4.y, s[i + 1], b1); b0 = fmaf(q4.z, s[i + 2], b0); b1 = fmaf(q4.w, s[i + 3], b1);
+          for (int i = 0; i < NR; i += 4) {
+            const float4 k4 = kp[i >> 2], q4 = qp[i >> 2];
+            a0 = fmaf(k4.x, s[i], a0); a1 = fmaf(k4.y, s[i + 1], a1); a0 = fmaf(k4.z, s[i + 2], a0); a1 = fmaf(k4.w, s[i + 3], a1);
+            b0 = fmaf(q4.x, s[i], b0); b1 = fmaf(q4.y, s[i + 1], b1); b0 = fmaf(q4.z, s[i + 2], b0); b1 = fmaf(q4.w, s[i + 3], b1);
+          }
+          parts[(t * W + warp) * 32 + lane] = a0 + a1;
+          parts[((T + t) * W + warp) * 32 + lane] = b0 + b1;
         }
-        parts[(t * W + warp) * 32 + lane] = a0 + a1;
-        parts[((T + t) * W + warp) * 32 + lane] = b0 + b1;
+      __syncthreads();  // the parts are there
+      if (WHOLE || warp < cnt) {  // this warp adds the parts of token `warp`
+        float Pt = 0.f, Bt = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+          Pt += parts[(warp * W + w) * 32 + lane];
+          Bt += parts[((T + warp) * W + w) * 32 + lane];
+        }
+        sums[warp * 32 + lane] = Pt;
+        sums[(T + warp) * 32 + lane] = Bt;
       }
-    __syncthreads();  // the parts are there
-    if (warp < cnt) {  // this warp adds the parts of token `warp`
-      float Pt = 0.f, Bt = 0.f;
+      __syncthreads();  // P, B and the products are there
+      // the writes, one after another: scalars of this column only.  ud[x] = (c_t / c_x) u_x as token t sees it.
+      float ud[T];
+      float c = 1.f;
 #pragma unroll
-      for (int w = 0; w < W; ++w) {
-        Pt += parts[(warp * W + w) * 32 + lane];
-        Bt += parts[((T + warp) * W + w) * 32 + lane];
-      }
-      sums[warp * 32 + lane] = Pt;
-      sums[(T + warp) * 32 + lane] = Bt;
-    }
-    __syncthreads();  // P, B and the products are there
-    // the writes, one after another: scalars of this column only.  ud[x] = (c_t / c_x) u_x as token t sees it.
-    float ud[T];
-    float c = 1.f;
+      for (int t = 0; t < T; ++t) {
+        ud[t] = 0.f;
+        if (WHOLE || t < cnt) {
+          float mk[T], mq[T];
 #pragma unroll
-    for (int t = 0; t < T; ++t) {
-      ud[t] = 0.f;
-      if (t < cnt) {
-        float mk[T], mq[T];
+          for (int s4 = 0; s4 < T; s4 += 4) {
+            if (s4 < t) *reinterpret_cast<float4*>(mk + s4) = *reinterpret_cast<const float4*>(Mkk + t * T + s4);
+            if (s4 <= t) *reinterpret_cast<float4*>(mq + s4) = *reinterpret_cast<const float4*>(Mqk + t * T + s4);
+          }
+          const float g = gs[t];
+          c *= g;
+          float a = c * sums[t * 32 + lane];
 #pragma unroll
-        for (int s4 = 0; s4 < T; s4 += 4) {
-          if (s4 < t) *reinterpret_cast<float4*>(mk + s4) = *reinterpret_cast<const float4*>(Mkk + t * T + s4);
-          if (s4 <= t) *reinterpret_cast<float4*>(mq + s4) = *reinterpret_cast<const float4*>(Mqk + t * T + s4);
-        }
-        const float g = gs[t];
-        c *= g;
-        float a = c * sums[t * 32 + lane];
+          for (int x = 0; x < t; ++x) {
+            ud[x] *= g;
+            a = fmaf(mk[x], ud[x], a);
+          }
+          ud[t] = bs[t] * (vs[t * 32 + lane] - a);
+          if (t == warp) {  // this warp makes the token's o
+            float ov = c * sums[(T + t) * 32 + lane];
 #pragma unroll
-        for (int x = 0; x < t; ++x) {
-          ud[x] *= g;
-          a = fmaf(mk[x], ud[x], a);
-        }
-        ud[t] = bs[t] * (vs[t * 32 + lane] - a);
-        if (t == warp) {  // this warp makes the token's o
-          float ov = c * sums[(T + t) * 32 + lane];
-#pragma unroll
-          for (int x = 0; x <= t; ++x) ov = fmaf(mq[x], ud[x], ov);
-          if (col_ok) o[((size_t)(t0 + t) * H + hd) * dv + j] = ov;
-        }
-      }
-    }
-    // the state after the group: c = the group's whole decay, ud = every write decayed by the tokens after it
-#pragma unroll
-    for (int i = 0; i < NR; ++i) s[i] *= c;
-#pragma unroll
-    for (int t = 0; t < T; ++t)
-      if (t < cnt) {
-        const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
-#pragma unroll
-        for (int i = 0; i < NR; i += 4) {
-          const float4 k4 = kp[i >> 2];
-          s[i] = fmaf(k4.x, ud[t], s[i]); s[i + 1] = fmaf(k4.y, ud[t], s[i + 1]);
-          s[i + 2] = fmaf(k4.z, ud[t], s[i + 2]); s[i + 3] = fmaf(k4.w, ud[t], s[i + 3]);
+            for (int x = 0; x <= t; ++x) ov = fmaf(mq[x], ud[x], ov);
+            if (col_ok) o[((size_t)(t0 + t) * H + hd) * dv + j] = ov;
+          }
         }
       }
+      // the state after the group: c = the group's whole decay, ud = every write decayed by the tokens after it
+#pragma unroll
+      for (int i = 0; i < NR; ++i) s[i] *= c;
+#pragma unroll
+      for (int t = 0; t < T; ++t)
+        if (WHOLE || t < cnt) {
+          const float4* kp = reinterpret_cast<const float4*>(ks + t * dkp + i0);
+#pragma unroll
+          for (int i = 0; i < NR; i += 4) {
+            const float4 k4 = kp[i >> 2];
+            s[i] = fmaf(k4.x, ud[t], s[i]); s[i + 1] = fmaf(k4.y, ud[t], s[i + 1]);
+            s[i + 2] = fmaf(k4.z, ud[t], s[i + 2]); s[i + 3] = fmaf(k4.w, ud[t], s[i + 3]);
+          }
+        }
+    };
+    if (cnt == T) walk(std::true_type{});
+    else walk(std::false_type{});
   }
 #pragma unroll
   for (int i = 0; i < NR; ++i)

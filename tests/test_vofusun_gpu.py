@@ -550,7 +550,7 @@ def test_long_decoding_and_slots_used_again(folders):
         engine = _engine(folders[name], dtype, max_tokens=320, max_slots=1)
         for req in ({"a": toks}, {"b": other}):
             got, _ = H.run_trace(engine, H.trace_tail_decode(req, tail=300), record_routing=False)
-            VH.compare(folders[name], req, got, dtype)
+            VH.compare(folders[name], req, got, dtype, stray=3 if dtype == "bfloat16" else 0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
