@@ -58,6 +58,8 @@ struct PrepParams {
   float* decay;             // [N, H]
   int N, R, G, H, dk, dv, taps, act;
   float unit_eps, q_scale;
+  int vec;                  // 16-byte accesses are possible (prep_group4)
+  int pad_;
 };
 
 // The convolved and activated value of channel c at token row n.  `first` = the row of the request's first token in
@@ -98,6 +100,64 @@ __device__ __forceinline__ void prep_group(const PrepParams& P, size_t n, int fi
   }
 }
 
+// The same for sizes and addresses that allow 16-byte accesses (every head size, row length and column offset a
+// multiple of four floats): a lane takes four neighbouring channels at a time, so a tap costs one load per split
+// instead of four, and heads of up to 256 channels stay in registers between the sum of squares and the store.  A
+// channel's sum runs over its taps in the same order as above.
+__device__ __forceinline__ float4 rows_at4(const RowsView& v, size_t row, int col) {
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < v.splits; ++z) {
+    const float4 x = *reinterpret_cast<const float4*>(v.p + (size_t)z * v.split_stride + row * v.ld + col);
+    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  }
+  return s;
+}
+
+__device__ __forceinline__ void prep_group4(const PrepParams& P, size_t n, int first, int grp, const float* old) {
+  const int lane = threadIdx.x & 31;
+  const int C_qk = P.G * P.dk;
+  const bool is_q = grp < P.G, is_k = !is_q && grp < 2 * P.G;
+  const int size = (is_q || is_k) ? P.dk : P.dv;
+  const int c0 = is_q ? grp * P.dk : (is_k ? C_qk + (grp - P.G) * P.dk : 2 * C_qk + (grp - 2 * P.G) * P.dv);
+  const int C = 2 * C_qk + P.H * P.dv;
+  float* dst = is_q ? P.qo + (n * P.G + grp) * P.dk
+                    : (is_k ? P.ko + (n * P.G + (grp - P.G)) * P.dk : P.vo + (n * P.H + (grp - 2 * P.G)) * P.dv);
+  float4 acc[2];
+  acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < P.taps; ++j) {
+    const long long s = (long long)n - P.taps + 1 + j;
+    const bool fresh = s >= first;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int i = lane * 4 + 128 * h;
+      if (i < size) {
+        const float4 x = fresh ? rows_at4(P.proj, (size_t)s, c0 + i)
+                               : *reinterpret_cast<const float4*>(old + (size_t)(s - first + P.taps - 1) * C + c0 + i);
+        const float* w = P.conv_w + (size_t)(c0 + i) * P.taps + j;
+        acc[h].x = fmaf(w[0], x.x, acc[h].x);
+        acc[h].y = fmaf(w[P.taps], x.y, acc[h].y);
+        acc[h].z = fmaf(w[2 * P.taps], x.z, acc[h].z);
+        acc[h].w = fmaf(w[3 * P.taps], x.w, acc[h].w);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    if (lane * 4 + 128 * h < size) {
+      acc[h].x = delta_act(acc[h].x, P.act); acc[h].y = delta_act(acc[h].y, P.act);
+      acc[h].z = delta_act(acc[h].z, P.act); acc[h].w = delta_act(acc[h].w, P.act);
+      ss = fmaf(acc[h].x, acc[h].x, ss); ss = fmaf(acc[h].y, acc[h].y, ss);
+      ss = fmaf(acc[h].z, acc[h].z, ss); ss = fmaf(acc[h].w, acc[h].w, ss);
+    }
+  float inv = 1.f;
+  if (is_q || is_k) inv = (is_q ? P.q_scale : 1.f) / sqrtf(warp_sum(ss) + P.unit_eps);
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    if (lane * 4 + 128 * h < size)
+      *reinterpret_cast<float4*>(dst + lane * 4 + 128 * h) = make_float4(acc[h].x * inv, acc[h].y * inv, acc[h].z * inv, acc[h].w * inv);
+}
+
 __device__ __forceinline__ void prep_gates(const PrepParams& P, size_t n) {
   for (int h = threadIdx.x; h < P.H; h += blockDim.x) {
     const float b = rows_at(P.proj, n, P.b_col + h);
@@ -119,10 +179,14 @@ __global__ void __launch_bounds__(256) conv_unit_prep_kernel(const PrepParams P)
   const int C = 2 * P.G * P.dk + P.H * P.dv;
   float old[DELTA_MAX_TAPS];
   const int b = blockIdx.x;
+  const bool vec = P.vec != 0;
   if (b < P.N) {
     const int r = P.req_of_token[b];
     if (P.positions[b] - P.q_start[r] < P.taps - 1) return;
-    for (int g = warp; g < groups; g += nwarp) prep_group(P, b, 0, g, nullptr, old);  // never reaches before the portion
+    for (int g = warp; g < groups; g += nwarp) {  // never reaches before the portion
+      if (vec) prep_group4(P, b, 0, g, nullptr);
+      else prep_group(P, b, 0, g, nullptr, old);
+    }
     prep_gates(P, b);
     return;
   }
@@ -131,10 +195,28 @@ __global__ void __launch_bounds__(256) conv_unit_prep_kernel(const PrepParams P)
   float* st = P.conv_state + (size_t)P.slot_ids[r] * (P.taps - 1) * C;
   const int head = qlen < P.taps - 1 ? qlen : P.taps - 1;
   for (int i = 0; i < head; ++i) {
-    for (int g = warp; g < groups; g += nwarp) prep_group(P, (size_t)n0 + i, n0, g, st, old);
+    for (int g = warp; g < groups; g += nwarp) {
+      if (vec) prep_group4(P, (size_t)n0 + i, n0, g, st);
+      else prep_group(P, (size_t)n0 + i, n0, g, st, old);
+    }
     prep_gates(P, (size_t)n0 + i);
   }
   __syncthreads();  // every read of the old state is done
+  if (vec && P.taps <= 4) {  // four channels of a thread at a time: all loads, then the stores
+    for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+      float4 keep[3];
+#pragma unroll
+      for (int t = 0; t < 3; ++t)
+        if (t < P.taps - 1) {
+          const int s = qlen - (P.taps - 1) + t;
+          keep[t] = s >= 0 ? rows_at4(P.proj, (size_t)n0 + s, c) : *reinterpret_cast<const float4*>(st + (size_t)(t + qlen) * C + c);
+        }
+#pragma unroll
+      for (int t = 0; t < 3; ++t)
+        if (t < P.taps - 1) *reinterpret_cast<float4*>(st + (size_t)t * C + c) = keep[t];
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     for (int t = 0; t < P.taps - 1; ++t) old[t] = st[(size_t)t * C + c];
     for (int t = 0; t < P.taps - 1; ++t) {
@@ -161,6 +243,10 @@ JLX_API int jlx_conv_unit_prep(const RowsView* proj, int b_col, int a_col, const
   P.a_bias = a_bias; P.cu_q = cu_q; P.q_start = q_start; P.slot_ids = slot_ids; P.req_of_token = req_of_token;
   P.positions = positions; P.qo = qo; P.ko = ko; P.vo = vo; P.beta = beta; P.decay = decay;
   P.N = N; P.R = R; P.G = G; P.H = H; P.dk = dk; P.dv = dv; P.taps = taps; P.act = act; P.unit_eps = unit_eps; P.q_scale = q_scale;
+  const auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  P.vec = dk % 4 == 0 && dv % 4 == 0 && dk <= 256 && dv <= 256 && proj->ld % 4 == 0 && (proj->splits == 1 || proj->split_stride % 4 == 0) &&
+          al16(proj->p) && al16(qo) && al16(ko) && al16(vo) && (!conv_state || al16(conv_state));
+  P.pad_ = 0;
   const int groups = 2 * G + H;
   const int warps = groups < 8 ? groups : 8;
   JLX_CUDA(jlx_launch_pdl(conv_unit_prep_kernel, dim3(N + (taps > 1 ? R : 0)), dim3(warps * 32), 0, stream, P));

@@ -177,6 +177,34 @@ def delta_scan(a) -> dict:
             "GB/s": round((rows + states) / t / 1e9, 1), "GFLOP/s": round(N * H * dk * dv * 7 / t / 1e9, 1)}
 
 
+def conv_unit_prep(a) -> dict:
+    """The kernel in front of the delta rule's recurrence: ``requests`` requests of ``tokens`` tokens each in one launch."""
+    dev = "cuda"
+    N, H, G, dk, dv, taps = a.requests * a.tokens, a.heads, a.key_heads or a.heads, a.dim, a.vdim, a.taps
+    C = 2 * G * dk + H * dv
+    F = C + H * dv + 2 * H
+    proj = torch.randn(1, N, F, device=dev)
+    conv_w = torch.randn(C, taps, device=dev) * 0.5
+    conv_state = torch.zeros(a.requests, max(taps - 1, 1), C, device=dev)
+    rate_log, a_bias = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+    cu = (torch.arange(a.requests + 1, device=dev, dtype=torch.int32) * a.tokens).contiguous()
+    slots = torch.arange(a.requests, device=dev, dtype=torch.int32)
+    req = slots.repeat_interleave(a.tokens).contiguous()
+    start = torch.full((a.requests,), 100, device=dev, dtype=torch.int32)
+    pos = (torch.arange(a.tokens, device=dev, dtype=torch.int32).repeat(a.requests) + 100).contiguous()
+    qo, ko = torch.empty(N, G, dk, device=dev), torch.empty(N, G, dk, device=dev)
+    vo, beta, decay = torch.empty(N, H, dv, device=dev), torch.empty(N, H, device=dev), torch.empty(N, H, device=dev)
+
+    def run():
+        K.conv_unit_prep(K.rows_view(proj, 1, 0), C + H * dv, C + H * dv + H, conv_w, conv_state if taps > 1 else None, rate_log, a_bias,
+                         cu, start, slots, req, pos, qo, ko, vo, beta, decay, "silu", 1e-6, dk ** -0.5)
+
+    t = _time(run, a.reps, _flush(a))
+    moved = N * (2 * C + 4 * H) * 4
+    return {"kernel": "conv_unit_prep", "requests": a.requests, "tokens": a.tokens, "heads": H, "key_heads": G, "dim": dk, "vdim": dv,
+            "taps": taps, "us": round(t * 1e6, 1), "bytes": moved, "GB/s": round(moved / t / 1e9, 1)}
+
+
 def _flush(a):
     return None if a.no_flush else torch.empty(256 * 1024 * 1024 // 4, device="cuda")
 
@@ -184,14 +212,17 @@ def _flush(a):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan", "delta_scan"):
+    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan", "delta_scan", "conv_unit_prep"):
         p = sub.add_parser(name)
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
-        if name == "delta_scan":
+        if name == "conv_unit_prep":
+            p.add_argument("--taps", type=int, default=4)
+        if name in ("delta_scan", "conv_unit_prep"):
             p.add_argument("--key-heads", type=int, default=0, help="heads of q and k (0: as many as value heads)")
+        if name == "delta_scan":
             p.add_argument("--products-in-block", action="store_true", help="no launch ahead for the products between a group's keys and queries")
-        if name in ("decay_scan", "delta_scan"):
+        if name in ("decay_scan", "delta_scan", "conv_unit_prep"):
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--requests", type=int, default=1)
             p.add_argument("--heads", type=int, default=16)
@@ -222,7 +253,7 @@ def main(argv=None) -> int:
             p.add_argument("--swiglu", action="store_true", help="fused SiLU(gate) * up epilogue")
     a = ap.parse_args(argv)
     print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "decay_scan": decay_scan,
-                      "delta_scan": delta_scan}[a.what](a)))
+                      "delta_scan": delta_scan, "conv_unit_prep": conv_unit_prep}[a.what](a)))
     return 0
 
 
