@@ -544,7 +544,7 @@ JLX_API int jlx_delta_scan(const float* q, const float* k, const float* v, const
                            int H, int dk, int dv, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && R >= 0 && G > 0 && H > 0 && dk > 0 && dv > 0 && H % G == 0, "delta_scan: bad sizes N=%d R=%d G=%d H=%d dk=%d dv=%d", N,
               R, G, H, dk, dv);
-  JLX_REQUIRE(dk <= 256, "delta_scan: key size %d is above the supported maximum 256", dk);
+  JLX_REQUIRE(dk <= 512, "delta_scan: key size %d is above the supported maximum 512", dk);
   JLX_REQUIRE(H <= 65535 && R <= 65535, "delta_scan: too many heads or requests");
   JLX_REQUIRE(!gram || (req_of_token && ((uintptr_t)gram & 15) == 0), "delta_scan: the products' scratch needs a 16-byte boundary and the tokens' requests");
   if (R == 0 || N == 0) return 0;
@@ -561,6 +561,8 @@ JLX_API int jlx_delta_scan(const float* q, const float* k, const float* v, const
   if (nr <= 12) return launch_delta_scan<12>(DELTA_ARGS);
   if (nr <= 16) return launch_delta_scan<16>(DELTA_ARGS);
   if (nr <= 24) return launch_delta_scan<24>(DELTA_ARGS);
-  return launch_delta_scan<32>(DELTA_ARGS);
+  if (nr <= 32) return launch_delta_scan<32>(DELTA_ARGS);
+  if (nr <= 48) return launch_delta_scan<48>(DELTA_ARGS);
+  return launch_delta_scan<64>(DELTA_ARGS);
 #undef DELTA_ARGS
 }

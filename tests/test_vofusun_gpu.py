@@ -31,7 +31,7 @@ def _i32(v):
 
 # ------------------------------------------------------------------------------------- kernels alone
 @pytest.mark.parametrize("ahead", [False, True])
-@pytest.mark.parametrize("dk, dv, Hh, G", [(1, 1, 1, 1), (9, 5, 2, 2), (16, 8, 4, 2), (33, 70, 2, 1), (128, 128, 2, 2), (200, 40, 3, 1), (256, 33, 2, 2)])
+@pytest.mark.parametrize("dk, dv, Hh, G", [(1, 1, 1, 1), (9, 5, 2, 2), (16, 8, 4, 2), (33, 70, 2, 1), (128, 128, 2, 2), (200, 40, 3, 1), (256, 33, 2, 2), (300, 36, 1, 1), (512, 8, 2, 1)])
 def test_delta_scan_sizes_and_a_batch_of_unequal_requests(dk, dv, Hh, G, ahead):
     """Other sizes (one channel; three warps; more rows than a lane's registers at the smallest build; no multiple of
     anything; several heads on one key head) and three requests of unequal length in one launch, from states that are not

@@ -6,6 +6,7 @@ must not be disturbed by what the first left there.
 The file sorts last on purpose, so that a run that stops at the first failure has run every other test."""
 
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -42,6 +43,8 @@ def test_no_alloc_argmax_matches_the_ordinary_one_twice_in_a_row():
         torch.cuda.synchronize()
         # Free memory as the driver counts it (cudaMemGetInfo): a cudaMalloc inside the library would show here,
         # while torch's own counters only see torch's allocator.
+        # Nothing that earlier tests left behind is collected (and its tensors freed) between the two readings.
+        gc.collect()
         free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         rc = fn(logits.data_ptr(), M, V, V, got.data_ptr(), stream)
         assert rc == 0, lib.jlx_last_error().decode()
