@@ -109,8 +109,12 @@ def test_delta_scan_keeps_a_far_token_and_corrects_a_key_that_is_written_again()
     _close(state[1], S, 1e-5, "the state at the end")
 
 
-@pytest.mark.parametrize("taps, G, Hh, dk, dv, splits", [(1, 1, 2, 8, 4, 1), (2, 2, 2, 5, 9, 2), (4, 1, 3, 32, 16, 1), (7, 3, 3, 24, 4, 3)])
-def test_short_convolution_unit_vectors_and_gates_in_portions(taps, G, Hh, dk, dv, splits):
+@pytest.mark.parametrize("taps, G, Hh, dk, dv, splits, front", [
+    (1, 1, 2, 8, 4, 1, 2), (2, 2, 2, 5, 9, 2, 2), (4, 1, 3, 32, 16, 1, 2), (7, 3, 3, 24, 4, 3, 2),
+    # rows whose length and offset allow 16-byte loads: four taps, more taps than the move keeps in registers, heads of more
+    # than 128 channels (a lane's second round, partly filled)
+    (4, 2, 4, 32, 16, 2, 4), (7, 1, 2, 24, 8, 3, 4), (3, 2, 2, 256, 132, 1, 8), (1, 1, 2, 8, 4, 1, 4)])
+def test_short_convolution_unit_vectors_and_gates_in_portions(taps, G, Hh, dk, dv, splits, front):
     """The kernel in front of the recurrence, fed two requests in portions (shorter than the taps reach, single tokens,
     long ones) beside each other, from split partial sums: convolution over each request's own time axis with its last
     inputs carried as state, silu, unit vectors (q scaled), the step and the decay, against the plain functions on the
@@ -124,7 +128,7 @@ def test_short_convolution_unit_vectors_and_gates_in_portions(taps, G, Hh, dk, d
     C = 2 * G * dk + Hh * dv
     F = C + Hh * dv + 2 * Hh  # q, k, v, the output gate's columns (not read here), step, decay
     lens = (37, 12)
-    proj = [torch.randn(splits, n, F + 2, device=DEV) for n in lens]  # two columns in front belong to something else
+    proj = [torch.randn(splits, n, F + front, device=DEV) for n in lens]  # the columns in front belong to something else
     conv_w = torch.randn(C, taps, device=DEV) * 0.5
     rate_log, a_bias = torch.randn(Hh, device=DEV) * 0.5, torch.randn(Hh, device=DEV)
     conv_state = torch.zeros(3, max(taps - 1, 1), C, device=DEV)
@@ -141,7 +145,7 @@ def test_short_convolution_unit_vectors_and_gates_in_portions(taps, G, Hh, dk, d
         qo, ko = torch.empty(N, G, dk, device=DEV), torch.empty(N, G, dk, device=DEV)
         vo, b, d = torch.empty(N, Hh, dv, device=DEV), torch.empty(N, Hh, device=DEV), torch.empty(N, Hh, device=DEV)
         ctx = _ctx(rt, ns, [at[r] for r in live], [slots[r] for r in live])
-        K.conv_unit_prep(K.rows_view(rows, splits, 2), C + Hh * dv, C + Hh * dv + Hh, conv_w, conv_state if taps > 1 else None, rate_log,
+        K.conv_unit_prep(K.rows_view(rows, splits, front), C + Hh * dv, C + Hh * dv + Hh, conv_w, conv_state if taps > 1 else None, rate_log,
                          a_bias, ctx.cu_q, ctx.q_start, ctx.slot_ids, ctx.req_of_token, ctx.positions, qo, ko, vo, b, d, "silu", 1e-6,
                          dk ** -0.5)
         o = 0
@@ -152,7 +156,7 @@ def test_short_convolution_unit_vectors_and_gates_in_portions(taps, G, Hh, dk, d
             at[r] += n
     c = lambda t: t.double().cpu()
     for r, n in enumerate(lens):
-        s = c(proj[r].sum(0))[:, 2:]
+        s = c(proj[r].sum(0))[:, front:]
         y = plain.causal_conv_silu(s[:, :C], c(conv_w))
         qr = plain.unit_vector(y[:, :G * dk].view(n, G, dk)) * dk ** -0.5
         kr = plain.unit_vector(y[:, G * dk:2 * G * dk].view(n, G, dk))
