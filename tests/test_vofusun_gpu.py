@@ -508,6 +508,24 @@ def test_every_kind_of_cut_against_the_plain_implementation(folders, name, dtype
         assert engine.manager.free_slots() == 4 and all(engine.manager.free_pages(g) == engine.num_pages for g in range(len(engine.manager.groups)))
 
 
+@pytest.mark.parametrize("seed", [0, 1, 3, 5, 7, 8, 11, 13])
+def test_configurations_drawn_at_random_under_every_kind_of_cut(seed, tmp_path):
+    """Sizes, head counts, orders of layers, windows, chunks, taps, rotations and loops that nobody chose, in both precisions:
+    whole prompts, a decoded tail, portions and mixed batches against the plain implementation."""
+    import jax_llm_examples_b200 as J
+
+    rng = random.Random(seed)
+    cfg = VH.random_config(rng)
+    folder = J.write_random_model(tmp_path / "m", cfg, seed, norm_noise=0.1, std=0.15)
+    requests = H.random_requests(rng, cfg["vocab"], [70, 3, 130, 21, 45])
+    for dtype in ("float32", "bfloat16"):
+        engine = _engine(folder, dtype, max_tokens=20 * 16)
+        for steps in (H.trace_whole(requests), H.trace_tail_decode(requests, tail=40), H.trace_portions(requests, rng),
+                      H.trace_mixed(requests, rng, max_live=4)):
+            got, _ = H.run_trace(engine, steps, record_routing=False)
+            VH.compare(folder, requests, got, dtype, stray=4 if dtype == "bfloat16" else 0)
+
+
 @pytest.mark.parametrize("name", list(VH.CONFIGS))
 def test_logits_do_not_depend_on_the_cut_or_on_the_batch(folders, name):
     """float32: the same request whole, token by token, in portions, and beside three other requests gives the same

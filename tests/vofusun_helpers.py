@@ -80,6 +80,37 @@ CONFIGS = {
 }
 
 
+def random_config(rng) -> dict:
+    """A configuration drawn at random: two to six layers of the three mixers in any order, odd and even sizes, one to four
+    query heads per key head, windows and chunks from one token to more than a prompt, with and without rotation and
+    frequency scaling, layers without a feed-forward, and (mostly) a loop somewhere that runs one to three times."""
+    width = rng.choice([24, 40, 64, 96, 128])
+    def mlp():
+        return None if rng.random() < 0.2 else dense(rng.choice([16, 24, 72, 128]))
+    def att():
+        kv = rng.choice([1, 2, 3]); heads = kv * rng.choice([1, 2, 4])
+        return attention(heads, kv, rng.choice([8, 12, 16, 32, 64, 128]), rng.choice([8, 20, 16, 64, 128]), rng.choice([1, 2, 5, 16, 17, 31, 64, 100]), rng.uniform(0.05, 0.4), mlp())
+    def dl():
+        kv = rng.choice([1, 2, 3]); heads = kv * rng.choice([1, 2, 3])
+        return delta(heads, kv, rng.choice([4, 6, 16, 20, 32, 64]), rng.choice([4, 7, 16, 36, 64]), rng.choice([1, 2, 3, 4, 5]), mlp())
+    def at2():
+        kv = rng.choice([1, 2]); heads = kv * rng.choice([1, 2, 4]); dim = rng.choice([8, 16, 24, 64, 128])
+        rot = None
+        if rng.random() < 0.8:
+            dims = rng.choice([d for d in (2, 4, 8, dim // 2, dim) if d <= dim and d % 2 == 0])
+            scaling = None if rng.random() < 0.4 else (rng.choice([2.0, 8.0]), rng.choice([1.0, 2.0]), rng.choice([3.0, 4.0]), rng.choice([16, 64, 8192]))
+            rot = (rng.choice([100.0, 10000.0, 500000.0]), dims, scaling)
+        return attention_2(heads, kv, dim, rng.choice([1, 3, 8, 16, 20, 33, 64]), rng.uniform(0.05, 0.3), rot, mlp())
+    n = rng.randint(2, 6)
+    layers = [rng.choice([att, dl, at2])() for _ in range(n)]
+    cfg = {"architecture": "Vofusun", "vocab": rng.choice([37, 64, 100]), "width": width, "embedding": {"scale": rng.uniform(0.5, 4.0)},
+           "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    if rng.random() < 0.7:
+        a = rng.randint(0, n - 1); b = rng.randint(a + 1, n)
+        cfg["loop"] = {"start": a, "stop": b, "times": rng.randint(1, 3)}
+    return cfg
+
+
 def config(name: str, **overrides) -> dict:
     c = copy.deepcopy(CONFIGS[name])
     c.update(overrides)
