@@ -11,10 +11,14 @@
 //                    channel over a request's time axis (the last taps - 1 inputs of a request are its state), an
 //                    activation, then q and k made unit vectors per head (q scaled), beta = sigmoid(b) and the decay
 //                    g = exp(-rate * softplus(a + bias)) per head.
-//   delta_scan       the recurrence over each request's tokens, in order; the state lives in registers.
+//   delta_gram       the products between the keys and queries of each group of DELTA_TB tokens, once per key head
+//                    (steps that hold prompts).
+//   delta_scan       the recurrence over each request's tokens, a group at a time; the state lives in registers.
 //
-// Every sum runs in an order that depends on the token alone, so a token's result does not change with the batch or
-// with how its prompt was cut into steps.
+// Nothing of another request enters a token's sums, so a token's result does not change with the batch.  In
+// conv_unit_prep the order of a sum depends on the token alone; in delta_scan it also depends on where the token stands
+// in its group, and groups count from the request's first token of the step: cutting a prompt elsewhere moves the
+// last bits of a result, no more.
 #include <type_traits>
 
 #include "common.cuh"
