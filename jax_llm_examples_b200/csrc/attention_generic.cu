@@ -10,6 +10,8 @@
 // 1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)).
 // With `sink` (one number per query head) the softmax has one more term in its denominator, exp(sink[h]), which
 // carries no value: weights p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); a sink of 0 adds one to the denominator.
+// With `slopes` (one number per query head) slopes[h] * (p - j) is taken off the scaled score of key j: a bias that
+// grows with the distance.
 // The order of the key loop depends only on (start, p): a position's result does not change with
 // what else is in the batch or how the prompt was cut into steps.
 #include "common.cuh"
@@ -24,7 +26,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                          T* __restrict__ out, int Hq, int Hkv, int dh, int page_size, int num_pages,
                                          float scale, int chunk, int window, float attn_scale, float floor_scale,
-                                         const float* __restrict__ sink, int* status) {
+                                         const float* __restrict__ sink, const float* __restrict__ slopes, int* status) {
   JLX_TL(TL_ATTN_GENERIC);
   extern __shared__ float smem[];
   const int n = blockIdx.x, hk = blockIdx.y;
@@ -51,6 +53,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     const int h = hk * G + g;
     if (active)
       for (int d = lane; d < dh; d += 32) qs[warp * dh + d] = to_f32<T>(q[((size_t)n * Hq + h) * dh + d]);
+    const float slope = slopes && active ? slopes[h] : 0.f;
     float m = -INFINITY, l = 0.f;
     float acc[ATT_MAX_D32];
 #pragma unroll
@@ -82,7 +85,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
           const float* kr = ks + lane * ldk;
           const float* qr = qs + warp * dh;
           for (int d = 0; d < dh; ++d) dot += qr[d] * kr[d];
-          s = dot * qscale;
+          s = fmaf(-slope, (float)(p - (t0 + lane)), dot * qscale);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);  // m = -inf on the first tile: exp(-inf) = 0
@@ -123,7 +126,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 JLX_API int jlx_attention_generic(const void* q, const void* pages, int dtype, const int* block_table, int bt_stride,
                                   const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv,
                                   int dh, int page_size, int num_pages, float scale, int chunk, int window,
-                                  float attn_scale, float floor_scale, const float* sink, int* status, cudaStream_t stream) {
+                                  float attn_scale, float floor_scale, const float* sink, const float* slopes, int* status,
+                                  cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && dh > 0 && page_size > 0 && num_pages > 0, "attention: bad sizes");
   JLX_REQUIRE(Hq % Hkv == 0, "attention: %d query heads are no multiple of %d KV heads", Hq, Hkv);
   JLX_REQUIRE(dh <= 32 * ATT_MAX_D32, "attention: head size %d is above the supported maximum %d", dh, 32 * ATT_MAX_D32);
@@ -138,7 +142,7 @@ JLX_API int jlx_attention_generic(const void* q, const void* pages, int dtype, c
       JLX_CUDA(cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attention_generic_kernel<T><<<dim3(N, Hkv), nwarp * 32, smem, stream>>>(
         (const T*)q, (const T*)pages, block_table, bt_stride, req_of_token, positions, (T*)out, Hq, Hkv, dh, page_size,
-        num_pages, scale, chunk, window, attn_scale, floor_scale, sink, status);
+        num_pages, scale, chunk, window, attn_scale, floor_scale, sink, slopes, status);
   });
   JLX_LAUNCH_CHECK("attention_generic");
   return 0;

@@ -87,7 +87,13 @@ struct AttnParams {
   const int* rows;      // optional, decode: the token rows to work on (null: rows 0..N-1); partials are indexed by the list's order
   int split_keys;       // keys per decode split (a multiple of SPLIT_UNIT)
   const float* sink;    // optional, [Hq]: one more term exp(sink[h]) in the softmax's denominator, without a value
+  const float* slopes;  // optional, [Hq]: slopes[h] * (query position - key position) is taken off the scaled score
 };
+
+// The slope of query head h in base-2 score units (0 without slopes).
+__device__ __forceinline__ float slope_log2(const AttnParams& P, int h, bool valid) {
+  return P.slopes && valid ? P.slopes[h] * 1.4426950408889634f : 0.f;
+}
 
 __device__ __forceinline__ int first_key(int p, int chunk, int window) {
   int s = 0;
@@ -183,6 +189,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     }
   }
   const float sc = P.scale_log2 * temperature(p, P.attn_scale, P.floor_scale);
+  const float sl[2] = {slope_log2(P, hk * G + (lane >> 2), (lane >> 2) < G), slope_log2(P, hk * G + (lane >> 2) + 8, (lane >> 2) + 8 < G)};
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   float o[DH / 8][4];
 #pragma unroll
@@ -218,7 +225,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
       for (int e = 0; e < 4; ++e) {
         const int key = tile_key + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
         const bool ok = key >= lo && key <= p;
-        s[nt][e] = ok ? s[nt][e] * sc : NEG_BIG;
+        s[nt][e] = ok ? fmaf(-sl[e >> 1], (float)(p - key), s[nt][e] * sc) : NEG_BIG;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
 #pragma unroll
@@ -398,6 +405,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   }
   JLX_TL_MARK(0);
   const float sc = P.scale_log2 * temperature(p, P.attn_scale, P.floor_scale);
+  const float sl[2] = {slope_log2(P, hk * G + (lane >> 2), (lane >> 2) < G), slope_log2(P, hk * G + (lane >> 2) + 8, (lane >> 2) + 8 < G)};
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   float o[DH / 8][4];
 #pragma unroll
@@ -434,7 +442,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
       for (int e = 0; e < 4; ++e) {
         const int key = tile_key + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
         const bool in = key >= lo && key <= p;
-        s[nt][e] = in ? s[nt][e] * sc : NEG_BIG;
+        s[nt][e] = in ? fmaf(-sl[e >> 1], (float)(p - key), s[nt][e] * sc) : NEG_BIG;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
 #pragma unroll
@@ -616,6 +624,7 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams
   }
   const float sc0 = P.scale_log2 * temperature(p0, P.attn_scale, P.floor_scale);
   const float sc1 = P.scale_log2 * temperature(p1, P.attn_scale, P.floor_scale);
+  const float slope = slope_log2(P, hk * G + warp, true);
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   float o[DH / 8][4];
 #pragma unroll
@@ -659,7 +668,7 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams
         for (int e = 0; e < 4; ++e) {
           const int key = tile_key + nt * 8 + (lane & 3) * 2 + (e & 1);
           const bool ok = (e < 2) ? (row0 && key >= lo0 && key <= p0) : (row1 && key >= lo1 && key <= p1);
-          s[nt][e] = ok ? s[nt][e] * ((e < 2) ? sc0 : sc1) : NEG_BIG;
+          s[nt][e] = ok ? fmaf(-slope, (float)(((e < 2) ? p0 : p1) - key), s[nt][e] * ((e < 2) ? sc0 : sc1)) : NEG_BIG;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
 #pragma unroll
@@ -797,6 +806,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
   }
   const float sc0 = P.scale_log2 * temperature(p0, P.attn_scale, P.floor_scale);
   const float sc1 = P.scale_log2 * temperature(p1, P.attn_scale, P.floor_scale);
+  const float slope = slope_log2(P, hk * G + warp, true);
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   float o[DH / 8][4];
 #pragma unroll
@@ -840,11 +850,9 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           bool in = true;
-          if (need_mask) {
-            const int key = tile_key + half * 32 + nt * 8 + (lane & 3) * 2 + (e & 1);
-            in = (e < 2) ? (row0 && key >= lo0 && key <= p0) : (row1 && key >= lo1 && key <= p1);
-          }
-          s[nt][e] = in ? s[nt][e] * ((e < 2) ? sc0 : sc1) : NEG_BIG;
+          const int key = tile_key + half * 32 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          if (need_mask) in = (e < 2) ? (row0 && key >= lo0 && key <= p0) : (row1 && key >= lo1 && key <= p1);
+          s[nt][e] = in ? fmaf(-slope, (float)(((e < 2) ? p0 : p1) - key), s[nt][e] * ((e < 2) ? sc0 : sc1)) : NEG_BIG;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
 #pragma unroll
@@ -913,7 +921,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
 // --------------------------------------------------------------------------------------- host
 static int fill_params(AttnParams& P, const void* q, const void* pages, const int* block_table, int bt_stride,
                        const int* req_of_token, const int* positions, void* out, int Hq, int Hkv, int dh, int page_size,
-                       int num_pages, float scale, int chunk, int window, float attn_scale, float floor_scale, const float* sink,
+                       int num_pages, float scale, int chunk, int window, float attn_scale, float floor_scale, const float* sink, const float* slopes,
                        int* status) {
   JLX_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d query heads are no multiple of %d KV heads", Hq, Hkv);
   JLX_REQUIRE(dh == 64 || dh == 128, "attention_mma: head size %d is not built (64 and 128 are); use the generic kernel", dh);
@@ -926,6 +934,7 @@ static int fill_params(AttnParams& P, const void* q, const void* pages, const in
   P.chunk = chunk; P.window = window; P.attn_scale = attn_scale; P.floor_scale = floor_scale; P.status = status;
   P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0; P.split_keys = SPLIT_UNIT; P.rows = nullptr;
   P.sink = sink;
+  P.slopes = slopes;
   return 0;
 }
 
@@ -1007,10 +1016,10 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
                                  const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv, int dh,
                                  int page_size, int num_pages, float scale, int chunk, int window, float attn_scale,
                                  float floor_scale, float* part_o, float* part_ml, int max_splits, int split_keys,
-                                 const int* rows, const float* sink, int* status, cudaStream_t stream) {
+                                 const int* rows, const float* sink, const float* slopes, int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
-                  scale, chunk, window, attn_scale, floor_scale, sink, status)) return 1;
+                  scale, chunk, window, attn_scale, floor_scale, sink, slopes, status)) return 1;
   JLX_REQUIRE(Hq / Hkv <= 16, "attention_decode: %d query heads per KV head; up to 16 are supported", Hq / Hkv);
   JLX_REQUIRE(part_o && part_ml && max_splits > 0, "attention_decode: scratch for the partial results is missing");
   JLX_REQUIRE(split_keys > 0 && split_keys % SPLIT_UNIT == 0, "attention_decode: split size %d is no multiple of %d", split_keys, SPLIT_UNIT);
@@ -1057,10 +1066,10 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
 JLX_API int jlx_attention_prefill(const void* q, const void* pages, const int* block_table, int bt_stride,
                                   const int* req_of_token, const int* positions, void* out, const int* tiles, int n_tiles,
                                   int Hq, int Hkv, int dh, int page_size, int num_pages, float scale, int chunk, int window,
-                                  float attn_scale, float floor_scale, const float* sink, int* status, cudaStream_t stream) {
+                                  float attn_scale, float floor_scale, const float* sink, const float* slopes, int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
-                  scale, chunk, window, attn_scale, floor_scale, sink, status)) return 1;
+                  scale, chunk, window, attn_scale, floor_scale, sink, slopes, status)) return 1;
   const int G = Hq / Hkv;
   JLX_REQUIRE(G <= 8, "attention_prefill: %d query heads per KV head; up to 8 are supported", G);
   JLX_REQUIRE(Hkv <= 65535, "attention_prefill: too many KV heads");

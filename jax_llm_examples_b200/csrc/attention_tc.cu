@@ -136,6 +136,7 @@ struct TcParams {
   float attn_scale, floor_scale;
   int* status;
   const float* sink;    // optional, [Hq]: one more term exp(sink[h]) in the softmax's denominator, without a value
+  const float* slopes;  // optional, [Hq]: slopes[h] * (query position - key position) is taken off the scaled score
 };
 
 __device__ __forceinline__ int first_key(int p, int chunk, int window) {
@@ -359,6 +360,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo_last = first_key(it.p_last, P.chunk, P.window);
       float sc = P.scale_log2;  // positive: raw scores and scaled scores have their maximum at the same key
       if (P.attn_scale != 0.f) sc *= 1.f + P.attn_scale * log1pf(floorf(((float)p_row + 1.f) / P.floor_scale));
+      // A distance bias in units of the RAW score (sc > 0): raw - bias_raw * (p - key) times sc is the biased scaled score,
+      // so the maximum and the exponents below work on it as they do on raw scores.
+      const bool biased = P.slopes != nullptr;
+      const float bias_raw = biased ? P.slopes[it.head] * 1.4426950408889634f / sc : 0.f;
       float m = NEG_BIG, l = 0.f;  // the running maximum (of scaled scores, in powers of two) and this thread's sum
       for (int j = 0; j < it.n_kv; ++j, ++g) {
         const int st = g & 1;
@@ -368,7 +373,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) break;
         tc_fence_after();
         const int tile_key = it.key_begin + j * BKV + col0;
-        const bool need_mask = it.key_begin + j * BKV + BKV - 1 > it.p_first || it.key_begin + j * BKV < lo_last;
+        const bool need_mask = biased || it.key_begin + j * BKV + BKV - 1 > it.p_first || it.key_begin + j * BKV < lo_last;
         const uint32_t s_addr = tm_s0 + st * 128 + lane_addr + col0;
         // this thread's raw scores of the row come into registers once
         uint32_t v[CP];
@@ -380,7 +385,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
           for (int c = 0; c < CP; ++c) {
             const int key = tile_key + c;
-            const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[c]) : NEG_BIG;
+            const float sv = (key >= lo_row && key <= p_row) ? fmaf(-bias_raw, (float)(p_row - key), __uint_as_float(v[c])) : NEG_BIG;
             v[c] = __float_as_uint(sv);
             mx4[c & 3] = fmaxf(mx4[c & 3], sv);
           }
@@ -551,7 +556,7 @@ JLX_API int jlx_attention_prefill_tc_supported(int Hq, int Hkv, int dh, int page
 JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int* block_table, int bt_stride,
                                      const int* req_of_token, const int* positions, void* out, const int* tiles,
                                      int n_tiles, int N, int Hq, int Hkv, int dh, int page_size, int num_pages, float scale,
-                                     int chunk, int window, float attn_scale, float floor_scale, const float* sink, int* status,
+                                     int chunk, int window, float attn_scale, float floor_scale, const float* sink, const float* slopes, int* status,
                                      cudaStream_t stream) {
   JLX_REQUIRE(jlx_attention_prefill_tc_supported(Hq, Hkv, dh, page_size),
               "attention_prefill_tc: needs head size 128 and pages of a multiple of 64 tokens (got %d, %d)", dh, page_size);
@@ -589,7 +594,7 @@ JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int
   P.block_table = block_table; P.bt_stride = bt_stride; P.req_of_token = req_of_token; P.positions = positions;
   P.out = (bf16*)out; P.tiles = tiles; P.Hq = Hq; P.Hkv = Hkv; P.page_size = page_size; P.num_pages = num_pages;
   P.scale_log2 = scale * 1.4426950408889634f; P.chunk = chunk; P.window = window; P.attn_scale = attn_scale;
-  P.floor_scale = floor_scale; P.status = status; P.sink = sink;
+  P.floor_scale = floor_scale; P.status = status; P.sink = sink; P.slopes = slopes;
   const size_t smem = 5 * (size_t)TILE_BYTES + 1024;
   static bool cfg = false;
   if (!cfg) {

@@ -11,7 +11,9 @@
 //                      [D] across steps, zeros at the start); the step's last h of a request becomes its state.
 //                      It can also write the row offsets m * N of the blends (groups of a grouped product).
 //   decay_prep         q (scaled), k, v and the decay d of every token and head from projected rows (split-K partials
-//                      are added on the way); d = exp(-exp(z + b)) or sigmoid(z + b)^(1/tau).
+//                      are added on the way); d = exp(-exp(z + b)), sigmoid(z + b)^(1/tau), or a constant per head;
+//                      optionally q and k turned by the token's position on their first entries (rotate-half pairs)
+//                      before q_scale and k_scale are applied.
 //   decay_scan         the recurrence over each request's tokens, in order; the state lives in registers.
 //   head_norm_gate     each head's o divided by its root mean square, times a weight, times silu(gate), times a
 //                      constant, written into (a column range of) the rows that the output product reads.
@@ -88,22 +90,41 @@ JLX_API int jlx_token_shift_blend(const float* h, const float* mu, float* state,
 }
 
 // ------------------------------------------------------------------------------------------------ decay prep
-enum { DECAY_DOUBLE_EXP = 0, DECAY_SIGMOID_POWER = 1 };
+// DECAY_HEAD_CONSTANT: one fixed decay per head (head_decay [H]) for all its key channels and every token; z unused.
+enum { DECAY_DOUBLE_EXP = 0, DECAY_SIGMOID_POWER = 1, DECAY_HEAD_CONSTANT = 2 };
 
 // One block per (token, head).
 __global__ void decay_prep_kernel(RowsView q, RowsView k, RowsView v, RowsView z, const float* __restrict__ z_bias, int mode,
                                   float inv_tau, float q_scale, float* __restrict__ qo, float* __restrict__ ko,
-                                  float* __restrict__ d_out, float* __restrict__ vo, int H, int dk, int dv) {
+                                  float* __restrict__ d_out, float* __restrict__ vo, int H, int dk, int dv,
+                                  const float* __restrict__ head_decay, float k_scale, const float* __restrict__ inv_freq, int rot,
+                                  const int* __restrict__ positions) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t n = blockIdx.x;
   const int hd = blockIdx.y;
   const size_t at_k = (n * H + hd) * dk, at_v = (n * H + hd) * dv;
+  const int half = rot >> 1;
+  const float pos = rot > 0 ? (float)positions[n] : 0.f;
   for (int i = threadIdx.x; i < dk; i += blockDim.x) {
     const int c = hd * dk + i;
-    qo[at_k + i] = rows_at(q, n, c) * q_scale;
-    ko[at_k + i] = rows_at(k, n, c);
+    float qv = rows_at(q, n, c), kv = rows_at(k, n, c);
+    if (i < rot) {  // entry i turns with entry i +- rot / 2 by the angle position * inv_freq[i mod rot / 2]
+      const bool first = i < half;
+      const int partner = first ? c + half : c - half;
+      float sn, cs;
+      sincosf(pos * inv_freq[first ? i : i - half], &sn, &cs);
+      const float qp = rows_at(q, n, partner), kp = rows_at(k, n, partner);
+      qv = first ? qv * cs - qp * sn : qv * cs + qp * sn;
+      kv = first ? kv * cs - kp * sn : kv * cs + kp * sn;
+    }
+    qo[at_k + i] = qv * q_scale;
+    ko[at_k + i] = kv * k_scale;
+    if (mode == DECAY_HEAD_CONSTANT) {
+      d_out[at_k + i] = head_decay[hd];
+      continue;
+    }
     const float x = rows_at(z, n, c) + (z_bias ? z_bias[c] : 0.f);
     float d;
     if (mode == DECAY_DOUBLE_EXP) {
@@ -120,12 +141,17 @@ __global__ void decay_prep_kernel(RowsView q, RowsView k, RowsView v, RowsView z
 
 JLX_API int jlx_decay_prep(const RowsView* q, const RowsView* k, const RowsView* v, const RowsView* z, const float* z_bias,
                            int mode, float tau, float q_scale, float* qo, float* ko, float* d_out, float* vo, int N, int H,
-                           int dk, int dv, cudaStream_t stream) {
+                           int dk, int dv, const float* head_decay, float k_scale, const float* inv_freq, int rot,
+                           const int* positions, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && H > 0 && dk > 0 && dv > 0 && H <= 65535, "decay_prep: bad sizes N=%d H=%d dk=%d dv=%d", N, H, dk, dv);
-  JLX_REQUIRE(mode == DECAY_DOUBLE_EXP || (mode == DECAY_SIGMOID_POWER && tau > 0.f), "decay_prep: unknown decay form or tau <= 0");
+  JLX_REQUIRE(mode == DECAY_DOUBLE_EXP || (mode == DECAY_SIGMOID_POWER && tau > 0.f) || (mode == DECAY_HEAD_CONSTANT && head_decay),
+              "decay_prep: unknown decay form, tau <= 0, or the heads' constant decays are missing");
+  JLX_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || (inv_freq && positions)), "decay_prep: %d rotated entries of %d need frequencies and positions", rot, dk);
+  RowsView none = {nullptr, 0, 0, 0, 0};
+  if (!z) z = &none;
   if (N == 0) return 0;
   JLX_CUDA(jlx_launch_pdl(decay_prep_kernel, dim3(N, H), dim3(dk + dv >= 256 ? 128 : 64), 0, stream, *q, *k, *v, *z, z_bias, mode,
-                          mode == DECAY_SIGMOID_POWER ? 1.f / tau : 0.f, q_scale, qo, ko, d_out, vo, H, dk, dv));
+                          mode == DECAY_SIGMOID_POWER ? 1.f / tau : 0.f, q_scale, qo, ko, d_out, vo, H, dk, dv, head_decay, k_scale, inv_freq, rot, positions));
   JLX_LAUNCH_CHECK("decay_prep");
   return 0;
 }

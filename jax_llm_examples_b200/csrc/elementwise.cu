@@ -600,9 +600,22 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
 // out[i, f] = silu(gate) * up of row i (llama4/llama4_jax/model.py:1146-1151).  The input row holds 2F values,
 // either [gate(0..F), up(0..F)] or, interleaved, blocks of [16 gate, 16 up]; it may come as `splits` float32
 // split-K partials that are added first.
+// The gated activation in its general form: act = g sigmoid(alpha g) (u + shift), with g = min(gate, limit) and
+// u = clamp(up, -limit, limit) when limit > 0.  alpha = 1, shift = 0, no limit: silu(gate) * up.
+struct GluForm {
+  float alpha, limit, shift;
+};
+__device__ __forceinline__ float glu_act(float g, float u, const GluForm& f) {
+  if (f.limit > 0.f) {
+    g = fminf(g, f.limit);
+    u = fminf(fmaxf(u, -f.limit), f.limit);
+  }
+  return g / (1.f + expf(-f.alpha * g)) * (u + f.shift);
+}
+
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
-                                int F, int interleaved) {
+                                int F, int interleaved, GluForm form) {
   JLX_TL(TL_SILU_MUL);
   const int i = blockIdx.x;
   const TI* g = gu + (size_t)i * 2 * F;
@@ -614,13 +627,12 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long
       a += to_f32<TI>(g[(size_t)z * split_stride + gi]);
       b += to_f32<TI>(g[(size_t)z * split_stride + ui]);
     }
-    const float s = a / (1.f + expf(-a));
-    out[(size_t)i * F + f] = from_f32<TO>(s * b);
+    out[(size_t)i * F + f] = from_f32<TO>(glu_act(a, b, form));
   }
 }
 
 // The common case in prompts: bfloat16 in and out, no partials; eight outputs per thread with 16-byte accesses.
-__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int F, int interleaved) {
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int F, int interleaved, GluForm form) {
   JLX_TL(TL_SILU_MUL);
   const size_t i = blockIdx.x;
   const bf16* g = gu + i * 2 * F;
@@ -635,26 +647,27 @@ __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __rest
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 x = __bfloat1622float2(ap[j]), y = __bfloat1622float2(bp[j]);
-      op[j] = __floats2bfloat162_rn(x.x / (1.f + expf(-x.x)) * y.x, x.y / (1.f + expf(-x.y)) * y.y);
+      op[j] = __floats2bfloat162_rn(glu_act(x.x, y.x, form), glu_act(x.y, y.y, form));
     }
     *reinterpret_cast<uint4*>(out + i * F + f0) = o;
   }
 }
 
 JLX_API int jlx_silu_mul(const void* gu, int in_dtype, int splits, long long split_stride, void* out, int out_dtype,
-                         int rows, int F, int interleaved, cudaStream_t stream) {
+                         int rows, int F, int interleaved, float alpha, float limit, float shift, cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && F > 0 && splits >= 1, "silu_mul: bad sizes rows=%d F=%d splits=%d", rows, F, splits);
+  const GluForm form = {alpha, limit, shift};
   JLX_REQUIRE(!interleaved || F % 16 == 0, "silu_mul: the interleaved layout needs a width that is a multiple of 16");
   JLX_REQUIRE(splits == 1 || in_dtype == JLX_F32, "silu_mul: split-K partials are float32");
   if (rows == 0) return 0;
   if (in_dtype == JLX_BF16 && out_dtype == JLX_BF16 && splits == 1 && F % 16 == 0 && ((uintptr_t)gu & 15) == 0 &&
       ((uintptr_t)out & 15) == 0) {
-    silu_mul_bf16x8_kernel<<<rows, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, interleaved);
+    silu_mul_bf16x8_kernel<<<rows, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, interleaved, form);
     JLX_LAUNCH_CHECK("silu_mul");
     return 0;
   }
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(out_dtype, TO,
-      (silu_mul_kernel<TI, TO><<<rows, 256, 0, stream>>>((const TI*)gu, splits, split_stride, (TO*)out, F, interleaved))));
+      (silu_mul_kernel<TI, TO><<<rows, 256, 0, stream>>>((const TI*)gu, splits, split_stride, (TO*)out, F, interleaved, form))));
   JLX_LAUNCH_CHECK("silu_mul");
   return 0;
 }

@@ -11,7 +11,7 @@
 // walking the experts and then the tiles was a third of the sort kernel's time in a decode step).
 __device__ __forceinline__ void expert_offsets_and_tiles(int* counts, int E, int P, int extra_rows, int tile_rows,
                                                          int* __restrict__ offsets, int* __restrict__ tile_list,
-                                                         int* __restrict__ n_tiles, int* status, bool real) {
+                                                         int* __restrict__ n_tiles, int* status, bool real, int tile_groups = 0) {
   const int lane = threadIdx.x & 31;
   int run = 0;
   for (int e0 = 0; e0 < E; e0 += 32) {
@@ -41,7 +41,10 @@ __device__ __forceinline__ void expert_offsets_and_tiles(int* counts, int E, int
   __syncwarp();
   if (tile_rows > 0) {
     // the tiles of group g follow those of the groups before it: the same scan over the groups' tile counts
-    const int groups = extra_rows > 0 ? E + 1 : E;
+    // tile_groups > 0: only the first so many groups get tiles (the others have no weights: experts that hand their
+    // input on unchanged are sorted with the rest, and the grouped products must not see them)
+    const int all_groups = extra_rows > 0 ? E + 1 : E;
+    const int groups = tile_groups > 0 && tile_groups < all_groups ? tile_groups : all_groups;
     int t_run = 0;
     for (int g0 = 0; g0 < groups; g0 += 32) {
       const int g = g0 + lane;

@@ -144,6 +144,7 @@ struct StreamArgs {
   void* out;             // [rows, N] (bf16 or f32), or partials [splits][rows][N] f32 when splits > 1
   int out_is_f32;
   int silu;              // 1: rows come in blocks of [16 gate, 16 up]; out[m, j] = silu(gate_j) * up_j, [rows, N / 2]
+  float glu_alpha, glu_limit, glu_shift;  // the gated activation's form: g sigmoid(alpha g) (u + shift), g and u clipped at +-limit (g from above only) when limit > 0
   int splits;
   int k_per_split;       // multiple of BK
   int offsets_settled;   // grouped: offsets and tile list were complete before the kernel in front of this one began its work
@@ -191,7 +192,12 @@ __device__ __forceinline__ void stream_epilogue(const StreamArgs& args, int warp
             const float gate = upper ? got : mine, up = upper ? mine : got;
             const int m = row_lo + c0 + j + (upper ? 1 : 0);
             if (m < row_hi) {  // N % 32 == 0: a block of 32 weight rows that starts below N lies wholly below it
-              const float act = __fdividef(gate, 1.f + __expf(-gate)) * up;
+              float gt = gate, uv = up;
+              if (args.glu_limit > 0.f) {
+                gt = fminf(gt, args.glu_limit);
+                uv = fminf(fmaxf(uv, -args.glu_limit), args.glu_limit);
+              }
+              const float act = __fdividef(gt, 1.f + __expf(-args.glu_alpha * gt)) * (uv + args.glu_shift);
               if (args.out_is_f32) ((float*)args.out)[(size_t)m * half_n + col] = act;
               else ((bf16*)args.out)[(size_t)m * half_n + col] = __float2bfloat16_rn(act);
             }
@@ -615,7 +621,8 @@ JLX_API int jlx_gemm_stream_token_tile(int rows_hint) { return pick_bt(rows_hint
 //         [splits * rows * N]) and a second kernel adds them in ascending order.
 // mode 1: out receives the float32 partials themselves, [splits][rows][N], for a consumer that adds them.
 // mode 2: fused SwiGLU epilogue: weight rows are interleaved in blocks of [16 gate, 16 up], out is
-//         [rows, N / 2] = silu(gate) * up; no split-K.
+//         [rows, N / 2] = silu(gate) * up; no split-K.  In general g sigmoid(glu_alpha g) (u + glu_shift) with
+//         g = min(gate, glu_limit), u = clamp(up, +-glu_limit) when glu_limit > 0; (1, 0, 0) is silu(gate) * up.
 // tile_list / n_tiles (optional, grouped only): the row tiles that have rows, made by jlx_expert_sort for the
 // tile width jlx_gemm_stream_token_tile(rows_hint); without them every block walks the offsets.
 // offsets_settled (grouped only): the caller's word that the kernel launched just before this one on the stream is a
@@ -624,7 +631,7 @@ JLX_API int jlx_gemm_stream_token_tile(int rows_hint) { return pick_bt(rows_hint
 JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_f32, int rows, int N, int K,
                             const int* offsets, int E, int rows_hint, int splits, float* scratch, int mode,
                             const int* tile_list, const int* n_tiles, int offsets_settled, int* splits_used, int* status,
-                            cudaStream_t stream) {
+                            float glu_alpha, float glu_limit, float glu_shift, cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && N > 0 && K > 0, "gemm_stream: bad sizes rows=%d N=%d K=%d", rows, N, K);
   JLX_REQUIRE(K % 8 == 0, "gemm_stream: K = %d is no multiple of 8 (TMA needs 16-byte row strides); use the SIMT product", K);
   JLX_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_stream: operands must be 16-byte aligned");
@@ -651,7 +658,7 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   a.N = N; a.K = K; a.rows = rows; a.offsets = offsets; a.E = E;
   a.tile_list = offsets ? tile_list : nullptr; a.n_tiles = n_tiles;
   a.out = (splits > 1 && mode == 0) ? (void*)scratch : out;
-  a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.splits = splits; a.k_per_split = kps; a.status = status;
+  a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.glu_alpha = glu_alpha; a.glu_limit = glu_limit; a.glu_shift = glu_shift; a.splits = splits; a.k_per_split = kps; a.status = status;
   a.offsets_settled = offsets && offsets_settled;
   // Row tiles to launch blocks for.  Grouped: a group of r rows has ceil(r / bt) <= r / bt + 1 tiles and only a group
   // with rows has any, so there are at most rows / bt + min(E, rows) of them.  (A looser bound costs time: a block

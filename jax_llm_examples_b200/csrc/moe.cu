@@ -14,7 +14,7 @@
 // One block per token.  Warp w computes the scores of experts w, w + nwarp, ...: a fixed order of
 // the D products per (token, expert), so a token's routing does not depend on the batch.
 // bias (null: none) is added to the scores before the choice.  weight_form 0: sigmoid of the chosen score;
-// 1: softmax over the chosen scores only.
+// 1: softmax over the chosen scores only; 2: see RouterChoice.
 __device__ __forceinline__ void softmax_of_chosen(float* w, int k) {
   float m = -INFINITY, sum = 0.f;
   for (int j = 0; j < k; ++j) m = fmaxf(m, w[j]);
@@ -22,9 +22,92 @@ __device__ __forceinline__ void softmax_of_chosen(float* w, int k) {
   for (int j = 0; j < k; ++j) w[j] = expf(w[j] - m) / sum;
 }
 
+// What the choice needs beyond the scores, for weight_form 2 ("softmax over all, the chosen shares normalised"):
+// s = softmax(z) over all E outputs; the choice is made on s + correction, and only among the `keep` best of `groups`
+// equal groups of neighbouring outputs (a group's score: its largest s + correction; the others count as -inf, not
+// 0: corrections may be negative); the weights are the chosen s, divided by their sum (+ 1e-20), times `scale`.
+struct RouterChoice {
+  const float* correction;  // [E] or null
+  int groups, keep;         // groups <= 1: no limit
+  float scale;
+};
+
+// One thread: the k largest scores in order (strict comparison: the lower index wins a tie), their weights by form.
+// `sc` (shared memory, E entries) is used up.
+__device__ __forceinline__ void choose_experts(float* sc, int E, int k, int* __restrict__ idx, float* __restrict__ w, int weight_form,
+                                               const RouterChoice& ch) {
+  if (weight_form == 2) {
+    float m = -INFINITY, sum = 0.f;
+    for (int e = 0; e < E; ++e) m = fmaxf(m, sc[e]);
+    for (int e = 0; e < E; ++e) sum += expf(sc[e] - m);
+    // sc[e] <- the choice score; the share s is recomputed for the chosen from the logit kept in w's place below
+    const int per = ch.groups > 1 ? E / ch.groups : E;
+    unsigned long long allowed = ~0ull;  // bit g: group g may be chosen from (up to 64 groups)
+    if (ch.groups > 1 && ch.keep < ch.groups) {
+      allowed = 0ull;
+      for (int t = 0; t < ch.keep; ++t) {
+        int bg = -1;
+        float bv = 0.f;
+        for (int g = 0; g < ch.groups; ++g) {
+          if ((allowed >> g) & 1ull) continue;
+          float gv = -INFINITY;
+          for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, expf(sc[e] - m) / sum + (ch.correction ? ch.correction[e] : 0.f));
+          if (bg < 0 || gv > bv) {
+            bg = g;
+            bv = gv;
+          }
+        }
+        allowed |= 1ull << bg;
+      }
+    }
+    float total = 0.f;
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = 0.f, bs = 0.f;
+      for (int e = 0; e < E; ++e) {
+        if (isnan(sc[e]) || !((allowed >> (ch.groups > 1 ? e / per : 0)) & 1ull)) continue;
+        const float share = expf(sc[e] - m) / sum;
+        const float v = share + (ch.correction ? ch.correction[e] : 0.f);
+        if (best < 0 || v > bv) {
+          best = e;
+          bv = v;
+          bs = share;
+        }
+      }
+      if (best < 0) {  // fewer allowed outputs than k, or all NaN: still a valid index
+        best = j;
+        bs = 0.f;
+      }
+      idx[j] = best;
+      w[j] = bs;
+      total += bs;
+      sc[best] = NAN;  // taken
+    }
+    for (int j = 0; j < k; ++j) w[j] = w[j] / (total + 1e-20f) * ch.scale;
+    return;
+  }
+  for (int j = 0; j < k; ++j) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < E; ++e) {
+      const float v = sc[e];
+      if (isnan(v)) continue;
+      if (best < 0 || v > bv) {  // strict: the lower index wins a tie
+        best = e;
+        bv = v;
+      }
+    }
+    if (best < 0) best = j;  // all NaN: still a valid expert index
+    idx[j] = best;
+    w[j] = weight_form == 1 ? bv : 1.f / (1.f + expf(-bv));
+    sc[best] = NAN;  // taken
+  }
+  if (weight_form == 1) softmax_of_chosen(w, k);
+}
+
 __global__ void router_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
                               float* __restrict__ topk_w, float* __restrict__ scores_out, int D, int E, int k,
-                              const float* __restrict__ bias, int weight_form) {
+                              const float* __restrict__ bias, int weight_form, RouterChoice choice) {
   JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_MAX_E];
   const int n = blockIdx.x;
@@ -40,25 +123,7 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
   __syncthreads();
   if (scores_out)
     for (int e = threadIdx.x; e < E; e += blockDim.x) scores_out[(size_t)n * E + e] = scores[e];
-  if (threadIdx.x == 0) {
-    for (int j = 0; j < k; ++j) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < E; ++e) {
-        const float v = scores[e];
-        if (isnan(v)) continue;
-        if (best < 0 || v > bv) {  // strict: the lower index wins a tie
-          best = e;
-          bv = v;
-        }
-      }
-      if (best < 0) best = j;  // all NaN: still a valid expert index
-      topk_idx[(size_t)n * k + j] = best;
-      topk_w[(size_t)n * k + j] = weight_form == 1 ? bv : 1.f / (1.f + expf(-bv));
-      scores[best] = NAN;  // taken
-    }
-    if (weight_form == 1) softmax_of_chosen(topk_w + (size_t)n * k, k);
-  }
+  if (threadIdx.x == 0) choose_experts(scores, E, k, topk_idx + (size_t)n * k, topk_w + (size_t)n * k, weight_form, choice);
 }
 
 // Many tokens (prompt portions): a block takes ROWS tokens, so that a router row that a warp fetches serves all
@@ -70,7 +135,8 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
 template <int EPW>
 __global__ void __launch_bounds__(256, 2)
 router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
-                   float* __restrict__ topk_w, int N, int D, int E, int k, const float* __restrict__ bias, int weight_form) {
+                   float* __restrict__ topk_w, int N, int D, int E, int k, const float* __restrict__ bias, int weight_form,
+                   RouterChoice choice) {
   JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_ROWS][ROUTER_MAX_E];
   pdl_launch_dependents();
@@ -110,45 +176,32 @@ router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_rout
   }
   __syncthreads();
   if (threadIdx.x < rows) {
-    float* sc = scores[threadIdx.x];
     const size_t n = (size_t)n0 + threadIdx.x;
-    for (int j = 0; j < k; ++j) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < E; ++e) {
-        const float v = sc[e];
-        if (isnan(v)) continue;
-        if (best < 0 || v > bv) {  // strict: the lower index wins a tie
-          best = e;
-          bv = v;
-        }
-      }
-      if (best < 0) best = j;  // all NaN: still a valid expert index
-      topk_idx[n * k + j] = best;
-      topk_w[n * k + j] = weight_form == 1 ? bv : 1.f / (1.f + expf(-bv));
-      sc[best] = NAN;  // taken
-    }
-    if (weight_form == 1) softmax_of_chosen(topk_w + n * k, k);
+    choose_experts(scores[threadIdx.x], E, k, topk_idx + n * k, topk_w + n * k, weight_form, choice);
   }
 }
 
 // many_rows: the kernel that shares router rows among eight tokens (another order of the sums than the
 // one-token kernel's: a caller whose results must not depend on the batch uses one of the two throughout).
 JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, float* topk_w, float* scores_out, int N,
-                       int D, int E, int k, int many_rows, const float* bias, int weight_form, cudaStream_t stream) {
-  JLX_REQUIRE(weight_form == 0 || weight_form == 1, "router: unknown weight form %d", weight_form);
+                       int D, int E, int k, int many_rows, const float* bias, int weight_form, const float* correction,
+                       int groups, int keep, float scale, cudaStream_t stream) {
+  JLX_REQUIRE(weight_form >= 0 && weight_form <= 2, "router: unknown weight form %d", weight_form);
+  JLX_REQUIRE(groups <= 1 || (weight_form == 2 && groups <= 64 && E % groups == 0 && keep >= 1 && keep <= groups),
+              "router: %d groups (keep %d) of %d outputs: the softmax-over-all form, equal groups, up to 64, keep in 1..groups", groups, keep, E);
+  const RouterChoice choice = {correction, groups, keep, scale};
   JLX_REQUIRE(N >= 0 && D > 0, "router: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(E >= 1 && E <= ROUTER_MAX_E, "router: %d experts; supported 1..%d", E, ROUTER_MAX_E);
   JLX_REQUIRE(k >= 1 && k <= E && k <= ROUTER_MAX_K, "router: top-%d of %d experts; supported k in 1..min(E, %d)", k, E, ROUTER_MAX_K);
   if (N == 0) return 0;
   if (many_rows && !scores_out && D % 4 == 0 && (((uintptr_t)h | (uintptr_t)w_router) & 15) == 0) {
     const dim3 grid((N + ROUTER_ROWS - 1) / ROUTER_ROWS);
-    if (E <= 16) JLX_CUDA(jlx_launch_pdl(router_rows_kernel<2>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form));
-    else JLX_CUDA(jlx_launch_pdl(router_rows_kernel<4>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form));
+    if (E <= 16) JLX_CUDA(jlx_launch_pdl(router_rows_kernel<2>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form, choice));
+    else JLX_CUDA(jlx_launch_pdl(router_rows_kernel<4>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form, choice));
     JLX_LAUNCH_CHECK("router_rows");
     return 0;
   }
-  router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k, bias, weight_form);
+  router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k, bias, weight_form, choice);
   JLX_LAUNCH_CHECK("router");
   return 0;
 }
@@ -164,7 +217,7 @@ JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, flo
 __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
                                    int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
                                    int tile_rows, int* __restrict__ tile_list, int* __restrict__ n_tiles, int* status,
-                                   int in_smem) {
+                                   int in_smem, int tile_groups) {
   JLX_TL(TL_SORT);
   __shared__ int counts[ROUTER_MAX_E + 1];
   extern __shared__ int staged[];  // the choices, when `in_smem`: both passes below walk them once per expert
@@ -192,7 +245,7 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
     }
     __syncthreads();
     if (warp == 0) {
-      expert_offsets_and_tiles(counts, E, P, extra_rows, tile_rows, offsets, tile_list, n_tiles, status, real);
+      expert_offsets_and_tiles(counts, E, P, extra_rows, tile_rows, offsets, tile_list, n_tiles, status, real, tile_groups);
       if (real) JLX_TL_MARK(1);
     }
     __syncthreads();
@@ -216,13 +269,15 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
 
 // tile_list: int [(ceil((P + extra_rows) / tile_rows) + groups) * 2]; n_tiles: int [1]; both unused if tile_rows == 0.
 JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair, int* sorted_pos, int P, int E,
-                            int extra_rows, int tile_rows, int* tile_list, int* n_tiles, int* status, cudaStream_t stream) {
+                            int extra_rows, int tile_rows, int* tile_list, int* n_tiles, int* status, int tile_groups,
+                            cudaStream_t stream) {
   JLX_REQUIRE(tile_rows == 0 || (tile_list && n_tiles), "expert_sort: tile list outputs missing");
+  JLX_REQUIRE(tile_groups >= 0 && (tile_groups == 0 || extra_rows == 0), "expert_sort: tiles for the first groups only, without an appended group");
   JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E && extra_rows >= 0, "expert_sort: bad sizes P=%d E=%d", P, E);
   const int warps = E < 32 ? E : 32;
   const int in_smem = (size_t)P * sizeof(int) <= 40 * 1024;
   JLX_CUDA(jlx_launch_pdl(expert_sort_kernel, dim3(1), dim3(warps * 32), in_smem ? (size_t)P * sizeof(int) : 0, stream, topk_idx,
-                          offsets, sorted_pair, sorted_pos, P, E, extra_rows, tile_rows, tile_list, n_tiles, status, in_smem));
+                          offsets, sorted_pair, sorted_pos, P, E, extra_rows, tile_rows, tile_list, n_tiles, status, in_smem, tile_groups));
   return 0;
 }
 
@@ -265,11 +320,13 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
 
 // delta[n, :] = sum_j (pair_w ? pair_w[n * k + j] : 1) * y[sorted_pos[n * k + j], :]  (+ y[extra_base + n, :] if extra_base >= 0: the appended
 // shared-expert group)  (+ shared[n, :]), where y and shared may be split-K partials [z][rows][D] that are
-// added first, z ascending; j ascending: a fixed order.
+// added first, z ascending; j ascending: a fixed order.  With topk_idx, a choice >= n_real is an expert without weights
+// that hands its input on: its row is h_rows[n, :] (float32 [N, D]) instead of a row of y.
 __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, long long y_stride, int extra_base,
                                    const float* __restrict__ shared, int splits, long long split_stride,
                                    const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k,
-                                   const float* __restrict__ pair_w) {
+                                   const float* __restrict__ pair_w, const int* __restrict__ topk_idx, int n_real,
+                                   const float* __restrict__ h_rows) {
   JLX_TL(TL_MOE_COMBINE);
   pdl_launch_dependents();
   pdl_wait();
@@ -289,6 +346,9 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
         const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
         if (pair_w) {  // the expert's OUTPUT is weighted: its partials are added first, then scaled
           float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (topk_idx && topk_idx[(size_t)n * k + j] >= n_real) {  // an expert that hands its input on unchanged
+            e = *reinterpret_cast<const float4*>(h_rows + (size_t)n * D + d);
+          } else
           for (int z = 0; z < y_splits; ++z) {
             const float4 v = *reinterpret_cast<const float4*>(y + (size_t)z * y_stride + row);
             e.x += v.x; e.y += v.y; e.z += v.z; e.w += v.w;
@@ -313,6 +373,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
       const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
       if (pair_w) {
         float e = 0.f;
+        if (topk_idx && topk_idx[(size_t)n * k + j] >= n_real) e = h_rows[(size_t)n * D + d];
+        else
         for (int z = 0; z < y_splits; ++z) e += y[(size_t)z * y_stride + row];
         s = fmaf(pair_w[(size_t)n * k + j], e, s);
         continue;
@@ -325,11 +387,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
 
 JLX_API int jlx_moe_combine(const float* y, int y_splits, long long y_stride, int extra_base, const float* shared,
                             int splits, long long split_stride, const int* sorted_pos, float* delta, int N, int D, int k,
-                            const float* pair_w, cudaStream_t stream) {
+                            const float* pair_w, const int* topk_idx, int n_real, const float* h_rows, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1 && y_splits >= 1, "moe_combine: bad sizes");
+  JLX_REQUIRE(!topk_idx || (pair_w && h_rows), "moe_combine: experts that hand their input on need the pairs' weights and the input rows");
   if (N == 0) return 0;
   const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;  // four columns per thread: 1024 columns per block
   JLX_CUDA(jlx_launch_pdl(moe_combine_kernel, dim3(N, ysplit), dim3(256), 0, stream, y, y_splits, y_stride, extra_base, shared,
-                          splits, split_stride, sorted_pos, delta, D, k, pair_w));
+                          splits, split_stride, sorted_pos, delta, D, k, pair_w, topk_idx, n_real, h_rows));
   return 0;
 }

@@ -386,7 +386,8 @@ JLX_API int jlx_kv_store(const void* k, const void* v, void* pages, int dtype, c
 //   norm:   y = x / sqrt(mean(x^2) + eps) (* w)   over the head's dk entries (w: [dk], shared by the heads, or null)
 //   halves: (y_i, y_(i + rot/2)) <- (y_i cos a - y_(i + rot/2) sin a,  y_(i + rot/2) cos a + y_i sin a),
 //   pairs:  (y_2i, y_(2i + 1))   <- (y_2i cos a - y_(2i + 1) sin a,    y_(2i + 1) cos a + y_2i sin a),
-//           a = position * inv_freq[i], i < rot / 2; entries from rot on pass unchanged.
+//           a = position * inv_freq[i], i < rot / 2; entries from rot on pass unchanged.  cos a and sin a are both
+//           multiplied by `amplitude` (1: a plain rotation).
 //
 // The projected rows are float32 (split-K partials are added first) with the q heads from column 0, the k heads from
 // column k_col and the v heads (dv entries each) from column v_col (v_col = k_col: the values are the keys as they
@@ -394,7 +395,9 @@ JLX_API int jlx_kv_store(const void* k, const void* v, void* pages, int dtype, c
 // up to it, so that one page layout and the attention kernels built for equal sizes serve keys of one size and values
 // of another.
 enum { ROPE_PAIRS_HALVES = 0, ROPE_PAIRS_INTERLEAVED = 1 };
-enum { ROPE_NORM_NONE = 0, ROPE_NORM_BEFORE = 1, ROPE_NORM_AFTER = 2 };
+// ROPE_NORM_WHOLE: before the rotation, over ALL heads of the projection at once: q / sqrt(mean over its Hq dk entries
+// + eps) * w, w: [Hq dk] ([Hkv dk] for k).
+enum { ROPE_NORM_NONE = 0, ROPE_NORM_BEFORE = 1, ROPE_NORM_AFTER = 2, ROPE_NORM_WHOLE = 3 };
 
 struct RopeRowsView {
   const float* p;
@@ -410,9 +413,10 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
                                           const int* __restrict__ positions, const float* __restrict__ q_norm_w,
                                           const float* __restrict__ k_norm_w, float eps, const float* __restrict__ inv_freq,
                                           int rot, int pairing, int norm_mode, int Hq, int Hkv, int dk, int dv, int dpad,
-                                          int page_size, int num_pages, int store, int* status) {
+                                          int page_size, int num_pages, int store, int* status, float amplitude) {
   JLX_TL(TL_ROPE);
   pdl_launch_dependents_if_small();
+  __shared__ float whole_part[2][8];
   extern __shared__ float buf[];  // [warps][2][max(dk, dv)]: a head's row as projected (and normed), and as rotated
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const size_t n = blockIdx.x;
@@ -432,6 +436,27 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
     }
   }
   const int heads = Hq + (store ? 2 * Hkv : 0);
+  float whole_rms[2] = {1.f, 1.f};  // of all q entries, of all k entries
+  if (norm_mode == ROPE_NORM_WHOLE) {
+    // every block of the token makes both sums itself, in an order fixed by the block's size (the model's head count)
+    for (int which = 0; which < (store ? 2 : 1); ++which) {
+      const int cnt = (which ? Hkv : Hq) * dk, col0 = which ? k_col : 0;
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < proj.splits; ++z) v += proj.p[(size_t)z * proj.split_stride + n * proj.ld + col0 + i];
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) whole_part[which][warp] = ss;
+    }
+    __syncthreads();
+    for (int which = 0; which < (store ? 2 : 1); ++which) {
+      float ss = 0.f;
+      for (int w = 0; w < nwarp; ++w) ss += whole_part[which][w];
+      whole_rms[which] = sqrtf(ss / (float)((which ? Hkv : Hq) * dk) + eps);
+    }
+  }
   for (int hh = blockIdx.y * nwarp + warp; hh < heads; hh += gridDim.y * nwarp) {
     const bool is_q = hh < Hq, is_k = !is_q && hh < Hq + Hkv;
     const bool qk = is_q || is_k;
@@ -454,6 +479,11 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
       const float rms = sqrtf(ss / (float)d + eps);
       __syncwarp();
       for (int i = lane; i < d; i += 32) row[i] = w ? row[i] / rms * w[i] : row[i] / rms;
+    } else if (qk && norm_mode == ROPE_NORM_WHOLE) {
+      const float rms = whole_rms[is_q ? 0 : 1];
+      const float* wh = w ? w + (size_t)(is_q ? hh : hh - Hq) * dk : nullptr;  // the weight covers the whole projection
+      __syncwarp();
+      for (int i = lane; i < d; i += 32) row[i] = wh ? row[i] / rms * wh[i] : row[i] / rms;
     }
     __syncwarp();
     float ss2 = 0.f;
@@ -466,6 +496,8 @@ __global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_co
         const int partner = pairing == ROPE_PAIRS_INTERLEAVED ? i ^ 1 : (first ? i + half : i - half);
         float sn, cs;
         sincosf((float)pos * inv_freq[f], &sn, &cs);
+        sn *= amplitude;
+        cs *= amplitude;
         y = first ? row[i] * cs - row[partner] * sn : row[i] * cs + row[partner] * sn;
       }
       turned[i] = y;
@@ -497,13 +529,13 @@ JLX_API int jlx_rope_half_kv_store(const RopeRowsView* proj, int k_col, int v_co
                                    const int* block_table, int bt_stride, const int* req_of_token, const int* positions,
                                    const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rot,
                                    int pairing, int norm_mode, int N, int Hq, int Hkv, int dk, int dv, int dpad, int page_size,
-                                   int num_pages, int store, int* status, cudaStream_t stream) {
+                                   int num_pages, int store, int* status, float amplitude, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && dk > 0 && dv > 0, "rope_half: bad sizes");
   JLX_REQUIRE(dpad >= dk && dpad >= dv, "rope_half: the padded head size %d is below the key or value size (%d, %d)", dpad, dk, dv);
   JLX_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk, "rope_half: %d rotated entries of %d", rot, dk);
   JLX_REQUIRE(rot == 0 || inv_freq, "rope_half: frequencies missing");
   JLX_REQUIRE(pairing == ROPE_PAIRS_HALVES || pairing == ROPE_PAIRS_INTERLEAVED, "rope_half: unknown pairing %d", pairing);
-  JLX_REQUIRE(norm_mode >= ROPE_NORM_NONE && norm_mode <= ROPE_NORM_AFTER, "rope_half: unknown norm mode %d", norm_mode);
+  JLX_REQUIRE(norm_mode >= ROPE_NORM_NONE && norm_mode <= ROPE_NORM_WHOLE, "rope_half: unknown norm mode %d", norm_mode);
   JLX_REQUIRE(!store || (pages && block_table && page_size > 0 && num_pages > 0), "rope_half: cache missing");
   if (N == 0) return 0;
   const int heads = Hq + (store ? 2 * Hkv : 0);
@@ -514,7 +546,7 @@ JLX_API int jlx_rope_half_kv_store(const RopeRowsView* proj, int k_col, int v_co
   JLX_DISPATCH_DTYPE(dtype, T, {
     JLX_CUDA(jlx_launch_pdl(rope_half_kv_store_kernel<T>, dim3(N, by), dim3(nwarp * 32), smem, stream, *proj, k_col, v_col,
                             (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token, positions, q_norm_w, k_norm_w, eps,
-                            inv_freq, rot, pairing, norm_mode, Hq, Hkv, dk, dv, dpad, page_size, num_pages, store, status));
+                            inv_freq, rot, pairing, norm_mode, Hq, Hkv, dk, dv, dpad, page_size, num_pages, store, status, amplitude));
   });
   JLX_LAUNCH_CHECK("rope_half_kv_store");
   return 0;

@@ -193,14 +193,59 @@ def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor | None, eps: float,
     return bool(did.value)
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: bool = False) -> None:
-    """out = silu(gate) * up.  gu: [rows, 2F] (or ``splits`` float32 partials [splits, rows, 2F]), laid out
-    [gate, up] or, interleaved, in blocks of [16 gate, 16 up]."""
+SILU_GLU = (1.0, 0.0, 0.0)  # (alpha, limit, shift) of the gated activation: silu(gate) * up
+
+
+def glu_form(alpha: float = 1.0, limit: float = 0.0, shift: float = 0.0) -> tuple[float, float, float]:
+    """The gated activation  g sigmoid(alpha g) (u + shift)  with g = min(gate, limit), u = clamp(up, -limit, limit)
+    when limit > 0: what ``silu_mul`` and the streaming product's epilogue take as ``glu``."""
+    if alpha <= 0 or limit < 0:
+        raise KernelError(f"gated activation: alpha {alpha} must be positive and limit {limit} not negative (0: none)")
+    return (float(alpha), float(limit), float(shift))
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: bool = False, glu=SILU_GLU) -> None:
+    """out = silu(gate) * up, or the gated activation ``glu`` (see :func:`glu_form`).  gu: [rows, 2F] (or ``splits``
+    float32 partials [splits, rows, 2F]), laid out [gate, up] or, interleaved, in blocks of [16 gate, 16 up]."""
     _contig(gu, out)
     rows, F = out.shape
     sp, stride = _splits(gu, splits)
     _run("elementwise", "jlx_silu_mul", _ptr(gu), c_int(code(gu.dtype)), c_int(sp), c_longlong(stride), _ptr(out),
-         c_int(code(out.dtype)), c_int(rows), c_int(F), c_int(int(interleaved)), _stream())
+         c_int(code(out.dtype)), c_int(rows), c_int(F), c_int(int(interleaved)), c_float(glu[0]), c_float(glu[1]), c_float(glu[2]),
+         _stream())
+
+
+# ------------------------------------------------------------------- several residual streams per token
+STREAMS_MAX = 8  # csrc/stream_mix.cu
+
+
+def stream_mix_norm(x: torch.Tensor, streams: int, *, first: torch.Tensor | None = None, y: torch.Tensor | None = None,
+                    y_splits: int = 1, mix: torch.Tensor | None = None, write: torch.Tensor | None = None,
+                    read: torch.Tensor | None = None, gamma: torch.Tensor | None = None, eps: float = 1e-6,
+                    out: torch.Tensor | None = None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None,
+                    sum_out: torch.Tensor | None = None) -> None:
+    """One pass over the S residual streams of every token, x float32 [N, S * D]:
+    with a pending sublayer output ``y`` (float32 [N, D] or ``y_splits`` partials):  x_t <- sum_s mix[s, t] x_s + write[t] y;
+    then  u = sum_t read[t] x_t  (``read`` None: the plain sum)  and  out / out32 = gamma * u / sqrt(mean(u^2) + eps).
+    ``first`` (float32 [N, D]): the streams were never written and all equal this row; they are written, not read.
+    With row_index, row n reads source row row_index[n] and x is not written back.  ``sum_out`` [n, D] gets the plain
+    sum of the new streams."""
+    _contig(x, first, y, mix, write, read, gamma, out, out32, row_index, sum_out)
+    S = int(streams)
+    if x.dim() != 2 or x.shape[1] % S:
+        raise KernelError(f"stream_mix_norm: rows of {x.shape[-1]} do not hold {S} streams")
+    D = x.shape[1] // S
+    n = row_index.numel() if row_index is not None else x.shape[0]
+    if any(t is not None and t.dtype != torch.float32 for t in (x, first, y, mix, write, read, gamma, out32, sum_out)):
+        raise KernelError("stream_mix_norm: streams, the pending output, the small weights and the norm weight must be float32")
+    if (mix is not None and mix.numel() != S * S) or any(t is not None and t.numel() != S for t in (write, read)):
+        raise KernelError(f"stream_mix_norm: {S} streams need a mix matrix of {S} x {S} and read and write weights of {S}")
+    if gamma is not None and gamma.numel() != D:
+        raise KernelError(f"stream_mix_norm: the norm weight has {gamma.numel()} entries for a width of {D}")
+    sp, stride = _splits(y, y_splits)
+    _run("stream_mix", "jlx_stream_mix_norm", _ptr(x), _ptr(first), _ptr(y), c_int(sp), c_longlong(stride), _ptr(mix), _ptr(write),
+         _ptr(read), _ptr(gamma), c_float(eps), _ptr(out), c_int(code(out.dtype) if out is not None else F32), _ptr(out32),
+         _ptr(row_index), _ptr(sum_out), c_int(n), c_int(S), c_int(D), _stream())
 
 
 # ------------------------------------------------------- grouped norms around a sublayer, biases, short convolution
@@ -464,21 +509,30 @@ def token_shift_blend(h32: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, 
          _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(slot_ids.numel()), c_int(D), c_int(M), _ptr(group_offsets), _stream())
 
 
-DECAY_FORMS = {"double_exp": 0, "sigmoid_power": 1}  # csrc/decay_scan.cu
+DECAY_FORMS = {"double_exp": 0, "sigmoid_power": 1, "head_constant": 2}  # csrc/decay_scan.cu
 
 
-def decay_prep(q: _RowsView, k: _RowsView, v: _RowsView, z: _RowsView, z_bias: torch.Tensor | None, form: str, tau: float,
+def decay_prep(q: _RowsView, k: _RowsView, v: _RowsView, z: _RowsView | None, z_bias: torch.Tensor | None, form: str, tau: float,
                q_scale: float, qo: torch.Tensor, ko: torch.Tensor, do: torch.Tensor, vo: torch.Tensor, heads: int, dk: int,
-               dv: int) -> None:
-    """qo = q_scale * q, ko = k, vo = v, do = the decay of every key channel: exp(-exp(z + bias)) ("double_exp") or
-    sigmoid(z + bias)^(1 / tau) ("sigmoid_power"), all float32 [N, H, dk] ([N, H, dv] for vo), from projected rows."""
-    _contig(z_bias, qo, ko, do, vo)
+               dv: int, head_decay: torch.Tensor | None = None, k_scale: float = 1.0, inv_freq: torch.Tensor | None = None,
+               rot_dims: int = 0, positions: torch.Tensor | None = None) -> None:
+    """qo = q_scale * q, ko = k_scale * k, vo = v, do = the decay of every key channel: exp(-exp(z + bias)) ("double_exp"),
+    sigmoid(z + bias)^(1 / tau) ("sigmoid_power") or ``head_decay[h]`` ("head_constant": float32 [H], no z), all float32
+    [N, H, dk] ([N, H, dv] for vo), from projected rows.  With ``rot_dims`` > 0, q and k are first turned on their first
+    rot_dims entries (entry i with i + rot_dims / 2) by the angle positions[n] * inv_freq[i]."""
+    _contig(z_bias, qo, ko, do, vo, head_decay, inv_freq, positions)
     N = qo.shape[0]
-    if any(t.dtype != torch.float32 for t in (qo, ko, do, vo)) or (z_bias is not None and z_bias.dtype != torch.float32):
-        raise KernelError("decay_prep: float32 outputs and bias are needed")
-    _run("decay_scan", "jlx_decay_prep", ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(z), _ptr(z_bias),
-         c_int(DECAY_FORMS[form]), c_float(tau), c_float(q_scale), _ptr(qo), _ptr(ko), _ptr(do), _ptr(vo), c_int(N), c_int(heads),
-         c_int(dk), c_int(dv), _stream())
+    if any(t.dtype != torch.float32 for t in (qo, ko, do, vo)) or any(
+            t is not None and t.dtype != torch.float32 for t in (z_bias, head_decay, inv_freq)):
+        raise KernelError("decay_prep: float32 outputs, bias, decays and frequencies are needed")
+    if form == "head_constant" and (head_decay is None or head_decay.numel() != heads):
+        raise KernelError(f"decay_prep: a constant decay per head needs {heads} numbers")
+    if rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2 or positions is None):
+        raise KernelError(f"decay_prep: {rot_dims} rotated entries need {rot_dims // 2} frequencies and the tokens' positions")
+    _run("decay_scan", "jlx_decay_prep", ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(z) if z is not None else None,
+         _ptr(z_bias), c_int(DECAY_FORMS[form]), c_float(tau), c_float(q_scale), _ptr(qo), _ptr(ko), _ptr(do), _ptr(vo), c_int(N),
+         c_int(heads), c_int(dk), c_int(dv), _ptr(head_decay), c_float(k_scale), _ptr(inv_freq), c_int(rot_dims), _ptr(positions),
+         _stream())
 
 
 def decay_scan(q: torch.Tensor, k: torch.Tensor, d: torch.Tensor, v: torch.Tensor, bonus: torch.Tensor | None, state: torch.Tensor,
@@ -570,21 +624,25 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
 
 # ---------------------------------- weighted q/k norm + rotate-half rotation + page write; gated attention heads
 ROPE_PAIRINGS = {"halves": 0, "pairs": 1}  # csrc/rope_kv.cu
-ROPE_NORMS = {"none": 0, "before": 1, "after": 2}
+ROPE_NORMS = {"none": 0, "before": 1, "after": 2, "whole": 3}
 
 
 def rope_norm_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
                        block_table: torch.Tensor | None, req_of_token: torch.Tensor, positions: torch.Tensor,
                        q_norm_weight: torch.Tensor | None, k_norm_weight: torch.Tensor | None, eps: float,
                        inv_freq: torch.Tensor | None, rot_dims: int, Hq: int, Hkv: int, dk: int, dv: int, status: torch.Tensor,
-                       pairing: str = "halves", norm: str = "before") -> None:
+                       pairing: str = "halves", norm: str = "before", amplitude: float = 1.0) -> None:
     """From projected float32 rows (q heads from the view's first column, k heads from column k_col, v heads of dv
     entries from v_col; v_col = k_col stores the keys as projected as values): q and k RMS-normed over dk (``norm``:
     "none", "before" or "after" the rotation; with a weight where one is given), their first rot_dims entries rotated
     (``pairing`` "halves": entry i with i + rot_dims / 2; "pairs": entry 2i with 2i + 1); q into q_out [N, Hq, dpad],
-    k and v into the token's cache row (pages [P, 2, Hkv, page_size, dpad]), all padded with zeros to dpad."""
+    k and v into the token's cache row (pages [P, 2, Hkv, page_size, dpad]), all padded with zeros to dpad.
+    ``norm`` "whole": before the rotation, over all heads of q (of k) at once, the weights [Hq dk] and [Hkv dk].
+    ``amplitude`` multiplies both the cosine and the sine of every angle."""
     _contig(q_out, pages, block_table, q_norm_weight, k_norm_weight, inv_freq)
     N, _, dpad = q_out.shape
+    if norm == "whole" and (q_norm_weight is None or k_norm_weight is None or q_norm_weight.numel() != Hq * dk or k_norm_weight.numel() != Hkv * dk):
+        raise KernelError(f"rope_norm_kv_store: a norm over the whole projection needs weights of {Hq * dk} and {Hkv * dk} entries")
     store = pages is not None
     if store and (pages.dtype != q_out.dtype or tuple(pages.shape[1:3]) != (2, Hkv) or pages.shape[4] != dpad):
         raise KernelError(f"rope_norm_kv_store: pages {tuple(pages.shape)} do not fit {Hkv} heads padded to {dpad}")
@@ -592,7 +650,8 @@ def rope_norm_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Ten
          c_int(code(q_out.dtype)), _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token),
          _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims),
          c_int(ROPE_PAIRINGS[pairing]), c_int(ROPE_NORMS[norm]), c_int(N), c_int(Hq), c_int(Hkv), c_int(dk), c_int(dv), c_int(dpad),
-         c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0), c_int(int(store)), _ptr(status), _stream())
+         c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0), c_int(int(store)), _ptr(status),
+         c_float(amplitude), _stream())
 
 
 def rope_half_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
@@ -648,11 +707,14 @@ def kv_store(k: torch.Tensor, v: torch.Tensor, pages: torch.Tensor, block_table:
 # ---------------------------------------------------------------------------------- attention
 def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                       positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int,
-                      attn_scale: float, floor_scale: float, status: torch.Tensor, sink: torch.Tensor | None = None) -> None:
+                      attn_scale: float, floor_scale: float, status: torch.Tensor, sink: torch.Tensor | None = None,
+                      slopes: torch.Tensor | None = None) -> None:
     """q: [N, Hq, dh]; pages: [P, 2, Hkv, page, dh]; out: [N, Hq, dh].  ``sink``: float32 [Hq] or None; with it the
-    softmax's denominator has one more term exp(sink[h]) that carries no value (all four attention kernels take it)."""
+    softmax's denominator has one more term exp(sink[h]) that carries no value.  ``slopes``: float32 [Hq] or None; with
+    it slopes[h] * (query position - key position) is taken off every scaled score (all four attention kernels take both)."""
     _contig(q, pages, block_table, out)
     _check_sink(sink, q.shape[1])
+    _check_sink(slopes, q.shape[1], "slopes")
     N, Hq, dh = q.shape
     P, _, Hkv, page_size, dh2 = pages.shape
     if dh2 != dh or pages.dtype != q.dtype:
@@ -660,12 +722,12 @@ def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.T
     _run("attention_generic", "jlx_attention_generic", _ptr(q), _ptr(pages), c_int(code(q.dtype)), _ptr(block_table),
          c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv),
          c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(slopes), _ptr(status), _stream())
 
 
-def _check_sink(sink: torch.Tensor | None, Hq: int) -> None:
+def _check_sink(sink: torch.Tensor | None, Hq: int, what: str = "sink") -> None:
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != Hq or not sink.is_contiguous()):
-        raise KernelError(f"attention: the sink must be float32 [{Hq}], one number per query head")
+        raise KernelError(f"attention: the {what} must be float32 [{Hq}], one number per query head")
 
 
 def attention_mma_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, decode: bool) -> bool:
@@ -685,7 +747,7 @@ def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Te
                      positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int, attn_scale: float,
                      floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int, split_keys: int,
                      status: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int = 0,
-                     sink: torch.Tensor | None = None) -> None:
+                     sink: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> None:
     """Split-KV attention for one query token per request (tensor cores, bfloat16).
     part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2].
     rows / n_rows: work on these token rows only (int32, the first n_rows entries): the single decoded tokens of
@@ -693,6 +755,7 @@ def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Te
     _contig(q, pages, block_table, out, part_o, part_ml, rows)
     N, Hq, dh = q.shape
     _check_sink(sink, Hq)
+    _check_sink(slopes, Hq, "slopes")
     if rows is not None:
         N = n_rows
     P, _, Hkv, page_size, _ = pages.shape
@@ -701,23 +764,24 @@ def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Te
     _run("attention_mma", "jlx_attention_decode", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size),
          c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale), c_float(floor_scale), _ptr(part_o),
-         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(rows), _ptr(sink), _ptr(status), _stream())
+         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(rows), _ptr(sink), _ptr(slopes), _ptr(status), _stream())
 
 
 def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                       positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
                       chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor,
-                      sink: torch.Tensor | None = None) -> None:
+                      sink: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> None:
     """Flash attention over the paged cache for prompt portions (tensor cores, bfloat16).
     tiles: int32 [n_tiles, 2] = (first token row, count <= 16), each within one request."""
     _contig(q, pages, block_table, out, tiles)
     N, Hq, dh = q.shape
     _check_sink(sink, Hq)
+    _check_sink(slopes, Hq, "slopes")
     P, _, Hkv, page_size, _ = pages.shape
     _run("attention_mma", "jlx_attention_prefill", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(Hq), c_int(Hkv), c_int(dh),
          c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(slopes), _ptr(status), _stream())
 
 
 def attention_prefill_tc_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, page_size: int) -> bool:
@@ -729,18 +793,19 @@ def attention_prefill_tc_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: 
 def attention_prefill_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                          positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
                          chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor,
-                         sink: torch.Tensor | None = None) -> None:
+                         sink: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> None:
     """Flash attention for prompt portions on tcgen05 (bfloat16, head size 128, pages of a multiple of 64).
     tiles: int32 [n_tiles, 2] = (first token row, count <= 128), each within one request; only the rows
     of these tiles are written."""
     _contig(q, pages, block_table, out, tiles)
     N, Hq, dh = q.shape
     _check_sink(sink, Hq)
+    _check_sink(slopes, Hq, "slopes")
     P, _, Hkv, page_size, _ = pages.shape
     _run("attention_tc", "jlx_attention_prefill_tc", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(N), c_int(Hq), c_int(Hkv),
          c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
-         c_float(floor_scale), _ptr(sink), _ptr(status), _stream())
+         c_float(floor_scale), _ptr(sink), _ptr(slopes), _ptr(status), _stream())
 
 
 # ------------------------------------------------------------------------------------- GEMMs
@@ -776,13 +841,14 @@ def gemm_stream_token_tile(rows_hint: int) -> int:
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
                 offsets: torch.Tensor | None = None, rows_hint: int = 0, splits: int = 1,
                 scratch: torch.Tensor | None = None, mode: int = GEMM_PLAIN,
-                tiles: tuple[torch.Tensor, torch.Tensor] | None = None, offsets_settled: bool = False) -> int:
+                tiles: tuple[torch.Tensor, torch.Tensor] | None = None, offsets_settled: bool = False, glu=SILU_GLU) -> int:
     """a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K]; w: [N, K] or,
     with row-group offsets [E + 1], [E, N, K].
     GEMM_PLAIN: out [M, N] bfloat16 or float32; splits > 1 cuts K across blocks (scratch: float32
     [splits * M * N]) and adds the partials.  GEMM_PARTIALS: out is float32 [splits, M, N], left for the
     consumer to add.  GEMM_SWIGLU: w's rows are interleaved [16 gate, 16 up]; out [M, N / 2] =
-    silu(gate) * up.  ``tiles`` = (tile_list, n_tiles) from expert_sort for the same rows_hint.
+    silu(gate) * up, or the gated activation ``glu`` (see :func:`glu_form`).  ``tiles`` = (tile_list, n_tiles) from
+    expert_sort for the same rows_hint.
     ``offsets_settled``: the kernel launched just before this call on the stream was a grouped gemm_stream over the
     same offsets and tiles (this one then finds its tile and asks for its weights without waiting for that one).
     Returns the split count used."""
@@ -803,36 +869,45 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: tor
     _run("gemm_stream", "jlx_gemm_stream", _ptr(a), _ptr(w), _ptr(out), c_int(int(out.dtype == torch.float32)), c_int(M),
          c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), c_int(mode),
          _ptr(tiles[0]) if tiles else None, _ptr(tiles[1]) if tiles else None, c_int(int(offsets_settled and offsets is not None)),
-         ctypes.byref(used), _ptr(status), _stream())
+         ctypes.byref(used), _ptr(status), c_float(glu[0]), c_float(glu[1]), c_float(glu[2]), _stream())
     return used.value
 
 
 # --------------------------------------------------------------------------------------- MoE
-ROUTER_WEIGHT_FORMS = {"sigmoid": 0, "softmax_of_chosen": 1}  # csrc/moe.cu
+ROUTER_WEIGHT_FORMS = {"sigmoid": 0, "softmax_of_chosen": 1, "softmax_normalized": 2}  # csrc/moe.cu
+ROUTER_MAX_GROUPS = 64
 
 
 def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
            scores_out: torch.Tensor | None = None, many_rows: bool = False, bias: torch.Tensor | None = None,
-           weight_form: str = "sigmoid") -> None:
+           weight_form: str = "sigmoid", correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1,
+           scale: float = 1.0) -> None:
     """Scores h32 @ w_router^T (+ bias) in 32-bit, top-k of the scores (lower index wins ties); the weights are the
     sigmoid of each chosen score, or (``weight_form`` "softmax_of_chosen") the softmax over the chosen scores only.
+    "softmax_normalized": s = softmax of the scores over ALL outputs; the choice is made on s + ``correction`` (float32
+    [E]), among the ``keep`` best of ``groups`` equal groups of neighbouring outputs only (a group's score is its largest
+    choice score); the weights are the chosen s divided by their sum and multiplied by ``scale``.
     ``many_rows``: the kernel that shares each router row among eight tokens (for prompt portions; its sums
     run in another order than the one-token kernel's)."""
     _contig(h32, w_router, topk_idx, topk_w, scores_out, bias)
     N, D = h32.shape
     E, k = w_router.shape[0], topk_idx.shape[1]
-    if h32.dtype != torch.float32 or w_router.dtype != torch.float32 or (bias is not None and bias.dtype != torch.float32):
-        raise KernelError("router: scores are computed from float32 input, weight and bias")
+    _contig(correction)
+    if h32.dtype != torch.float32 or w_router.dtype != torch.float32 or any(
+            t is not None and (t.dtype != torch.float32 or t.numel() != E) for t in (bias, correction)):
+        raise KernelError("router: scores are computed from float32 input, weight, bias and correction (one number per output)")
     _run("moe", "jlx_router", _ptr(h32), _ptr(w_router), _ptr(topk_idx), _ptr(topk_w), _ptr(scores_out), c_int(N),
-         c_int(D), c_int(E), c_int(k), c_int(int(many_rows)), _ptr(bias), c_int(ROUTER_WEIGHT_FORMS[weight_form]), _stream())
+         c_int(D), c_int(E), c_int(k), c_int(int(many_rows)), _ptr(bias), c_int(ROUTER_WEIGHT_FORMS[weight_form]),
+         _ptr(correction), c_int(groups), c_int(keep), c_float(scale), _stream())
 
 
 def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,
                 E: int, status: torch.Tensor, extra_rows: int = 0, tile_rows: int = 0,
-                tile_list: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None) -> None:
+                tile_list: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None, tile_groups: int = 0) -> None:
     """Counting sort of the (token, choice) pairs by expert.  offsets: [E + 1], or [E + 2] with extra_rows > 0:
     one more group of that many rows appended after the experts.  With tile_rows > 0 also the list of row
-    tiles of that height that hold rows: tile_list int32 [(ceil(rows / tile_rows) + groups) * 2], n_tiles [1]."""
+    tiles of that height that hold rows: tile_list int32 [(ceil(rows / tile_rows) + groups) * 2], n_tiles [1];
+    ``tile_groups`` > 0: tiles of the first so many groups only (the later ones are experts without weights)."""
     _contig(topk_idx, offsets, sorted_pair, sorted_pos, tile_list, n_tiles)
     if offsets.numel() < E + 1 + (extra_rows > 0):
         raise KernelError("expert_sort: offsets too short")
@@ -842,7 +917,7 @@ def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torc
             raise KernelError("expert_sort: tile list too short")
     _run("moe", "jlx_expert_sort", _ptr(topk_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(sorted_pos),
          c_int(topk_idx.numel()), c_int(E), c_int(extra_rows), c_int(tile_rows), _ptr(tile_list), _ptr(n_tiles),
-         _ptr(status), _stream())
+         _ptr(status), c_int(tile_groups), _stream())
 
 
 def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor | None, a_sorted: torch.Tensor, k: int,
@@ -856,16 +931,22 @@ def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Te
 
 
 def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int,
-                shared_splits: int = 1, y_splits: int = 1, extra_base: int = -1, pair_weights: torch.Tensor | None = None) -> None:
+                shared_splits: int = 1, y_splits: int = 1, extra_base: int = -1, pair_weights: torch.Tensor | None = None,
+                topk_idx: torch.Tensor | None = None, n_real: int = 0, h_rows: torch.Tensor | None = None) -> None:
     """delta = the sum of each token's expert rows (+ row extra_base + n of y: an appended shared group)
     (+ shared); y_sorted and shared may be split-K partials.  ``pair_weights`` (float32 [N, k]): each expert row is
-    multiplied by its (token, choice) weight as it is added (experts whose OUTPUT is weighted)."""
-    _contig(y_sorted, shared, sorted_pos, delta, pair_weights)
+    multiplied by its (token, choice) weight as it is added (experts whose OUTPUT is weighted).  With ``topk_idx``
+    (int32 [N, k]) a choice >= ``n_real`` is an expert without weights whose output is its input: the token's row of
+    ``h_rows`` (float32 [N, D]) takes the place of a row of y."""
+    _contig(y_sorted, shared, sorted_pos, delta, pair_weights, topk_idx, h_rows)
+    if h_rows is not None and (h_rows.dtype != torch.float32 or h_rows.shape != delta.shape):
+        raise KernelError("moe_combine: the input rows must be float32 [N, D]")
     N, D = delta.shape
     sp, stride = _splits(shared, shared_splits)
     ysp, ystride = _splits(y_sorted, y_splits)
     _run("moe", "jlx_moe_combine", _ptr(y_sorted), c_int(ysp), c_longlong(ystride), c_int(extra_base), _ptr(shared),
-         c_int(sp), c_longlong(stride), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D), c_int(k), _ptr(pair_weights), _stream())
+         c_int(sp), c_longlong(stride), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D), c_int(k), _ptr(pair_weights),
+         _ptr(topk_idx), c_int(n_real), _ptr(h_rows), _stream())
 
 
 # ---------------------------------------------------------------------------------- sampling

@@ -76,13 +76,14 @@ class PagedAttention(Mixer):
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)  # model.py:774
 
     sink: torch.Tensor | None = None
+    slopes: torch.Tensor | None = None  # [Hq]: slopes[h] * (query position - key position) is taken off the scaled scores
 
     @staticmethod
-    def _sink_vector(sink, n_heads: int) -> torch.Tensor | None:
+    def _sink_vector(sink, n_heads: int, what: str = "sink") -> torch.Tensor | None:
         if sink is None:
             return None
         if sink.numel() != n_heads:
-            raise ValueError(f"the sink has {sink.numel()} entries for {n_heads} query heads")
+            raise ValueError(f"the {what} has {sink.numel()} entries for {n_heads} query heads")
         return sink.to(torch.float32).contiguous()
 
     # Head sizes that the tensor-core attention kernels are built for: a model with another head size never
@@ -132,7 +133,7 @@ class PagedAttention(Mixer):
         part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
         K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
                            chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status,
-                           rows, n_rows, self.sink)
+                           rows, n_rows, self.sink, self.slopes)
 
     def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
         """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV for
@@ -158,16 +159,16 @@ class PagedAttention(Mixer):
                     # long portions on the tcgen05 kernel (128-token tiles), the short ones below
                     K.attention_prefill_tc(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
                                            ctx.arrays["attn_tiles_long"], count["attn_tiles_long"], self.scale, chunk, window,
-                                           attn_scale, floor_scale, ctx.status, self.sink)
+                                           attn_scale, floor_scale, ctx.status, self.sink, self.slopes)
                     tiles, n_tiles = ctx.arrays["attn_tiles_short"], count["attn_tiles_short"]
                     kinds = ("tc", "flash" if n_tiles else "", "split_kv" if count["attn_single_rows"] else "")
                     ctx.scratch.setdefault("attention_kernels", set()).add(tuple(k for k in kinds if k))
                 if n_tiles:
                     K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, tiles,
-                                        n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status, self.sink)
+                                        n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status, self.sink, self.slopes)
                 return
         K.attention_generic(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
-                            self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status, self.sink)
+                            self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status, self.sink, self.slopes)
 
 
 register_part("mixer", "paged_attention", PagedAttention)
@@ -184,8 +185,15 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
         out = W_o [ sigmoid(W_g h)_a * softmax(scale * q_a K^T) V  for every head a ]
 
     ``w_in``: the q, k, v and gate projections stacked in that order, [Hq dk + Hkv dk + Hkv dv + gate rows, D] (no v rows
-    with ``values_are_keys``; gate rows: Hq, Hq dv or none).  ``q_norm_weight`` / ``k_norm_weight``: [dk], shared by the
-    heads.  ``norm``: "before", "after" or "none"; None = "before" if a weight is given, else "none".  ``window``: a query
+    with ``values_are_keys``; no k and v rows with ``projects_kv`` False: the layer reads the pages that another layer
+    fills, with its own queries, mask, sink and slopes; gate rows: Hq, Hq dv or none).  ``q_norm_weight`` /
+    ``k_norm_weight``: [dk], shared by the heads.  ``norm``: "before", "after" or "none"; None = "before" if a weight is
+    given, else "none"; "whole": before the rotation, ONE norm over all heads of q (and one over all of k), weights
+    [Hq dk] and [Hkv dk].  ``rot_amplitude`` multiplies the cosine and the sine of every angle (a rotation that also
+    stretches the rotated entries).  ``slopes`` [Hq]: slopes[h] * (i - j) is taken off the scaled score of query i and key
+    j.  ``query_temperature`` (coef, every): queries at position p are multiplied by 1 + coef * ln(floor((p + 1) / every)
+    + 1).  ``keep_window``: pages are kept for a window of at least this many positions (a layer with a longer window
+    reads them; 0: for good).  ``window``: a query
     sees itself and the window - 1 positions before it; ``chunk``: the positions of its own chunk.  Keys, queries and
     values are kept at one padded size (``padded_dim`` >= max(dk, dv), zeros beyond their own): one page layout, and the
     attention kernels built for equal sizes, serve both.  It is a :class:`ProjectedMixer`: beside another mixer that
@@ -198,7 +206,9 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
                  scale: float, eps: float, q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
                  inv_freq: torch.Tensor | None = None, rot_dims: int = 0, window: int | None = None, chunk: int | None = None,
                  gated: bool = True, padded_dim: int | None = None, sink: torch.Tensor | None = None, pairing: str = "halves",
-                 norm: str | None = None, values_are_keys: bool = False, gate: str | None = None):
+                 norm: str | None = None, values_are_keys: bool = False, gate: str | None = None,
+                 rot_amplitude: float = 1.0, slopes: torch.Tensor | None = None, query_temperature: tuple[float, float] | None = None,
+                 projects_kv: bool = True, keep_window: int | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} KV heads")
         gate = ("head" if gated else "none") if gate is None else gate
@@ -207,21 +217,27 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
         if values_are_keys and value_dim != head_dim:
             raise ValueError(f"values that are the keys have the keys' size {head_dim}, not {value_dim}")
         gate_rows = {"none": 0, "head": n_heads, "channel": n_heads * value_dim}[gate]
-        rows = (n_heads + n_kv_heads) * head_dim + (0 if values_are_keys else n_kv_heads * value_dim) + gate_rows
+        kv_rows = n_kv_heads * head_dim + (0 if values_are_keys else n_kv_heads * value_dim) if projects_kv else 0
+        rows = n_heads * head_dim + kv_rows + gate_rows
         if w_in.shape[0] != rows or w_o.shape[1] != n_heads * value_dim or w_o.shape[0] != w_in.shape[1]:
             raise ValueError(f"attention weights do not fit: w_in {tuple(w_in.shape)}, w_o {tuple(w_o.shape)} for {n_heads}/"
-                             f"{n_kv_heads} heads of {head_dim} (values {value_dim}{', the keys' if values_are_keys else ''}) "
-                             f"with gate {gate!r}")
+                             f"{n_kv_heads} heads of {head_dim} (values {value_dim}{', the keys' if values_are_keys else ''}"
+                             f"{'' if projects_kv else '; keys and values are another layer\'s'}) with gate {gate!r}")
         if rot_dims % 2 or not 0 <= rot_dims <= head_dim or (rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2)):
             raise ValueError(f"{rot_dims} rotated entries of {head_dim} need {rot_dims // 2} frequencies")
-        for w in (q_norm_weight, k_norm_weight):
-            if w is not None and w.numel() != head_dim:
-                raise ValueError(f"a q/k norm weight has {w.numel()} entries for heads of {head_dim}")
         if (q_norm_weight is None) != (k_norm_weight is None):
             raise ValueError("q and k are normed with a weight each, or both without")
         self.norm = ("none" if q_norm_weight is None else "before") if norm is None else norm
         if self.norm not in K.ROPE_NORMS:
-            raise ValueError(f"norm {norm!r} is unknown (none, before, after)")
+            raise ValueError(f"norm {norm!r} is unknown (none, before, after, whole)")
+        for w, heads in ((q_norm_weight, n_heads), (k_norm_weight, n_kv_heads)):
+            want = heads * head_dim if self.norm == "whole" else head_dim  # "whole": one norm over all heads of the projection
+            if w is not None and w.numel() != want:
+                raise ValueError(f"a q/k norm weight has {w.numel()} entries; the norm {self.norm!r} of heads of {head_dim} takes {want}")
+        if self.norm == "whole" and q_norm_weight is None:
+            raise ValueError("the norm over a whole projection takes a weight for q and one for k")
+        if not projects_kv and keep_window is not None:
+            raise ValueError("a layer that reads another layer's keys and values keeps none itself")
         self.w_in, self.w_o = w_in, w_o
         self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim = n_heads, n_kv_heads, head_dim, value_dim
         self.head_dim = max(head_dim, value_dim) if padded_dim is None else int(padded_dim)  # what the cache and the kernels see
@@ -233,7 +249,21 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
         self.pairing, self.values_are_keys = pairing, bool(values_are_keys)
         self.chunk, self.window, self.scale = chunk, window, float(scale)
         self.sink = self._sink_vector(sink, n_heads)
+        self.slopes = self._sink_vector(slopes, n_heads, "slope vector")
+        self.rot_amplitude = float(rot_amplitude)
+        self.q_temperature = (0.0, 1.0) if query_temperature is None else (float(query_temperature[0]), float(query_temperature[1]))
+        if self.q_temperature[0] != 0.0 and self.q_temperature[1] <= 0:
+            raise ValueError("the query temperature's period must be positive")
+        self.projects_kv, self.keep_window = bool(projects_kv), keep_window
         self.position, self.qk_norm_eps = None, None
+
+    def kv_need(self) -> KVNeed:
+        need = PagedAttention.kv_need(self)
+        if self.keep_window is not None and self.window is not None and self.chunk is None:
+            # another layer reads these pages through a longer window (0: without one): keep them that long
+            keep = Retention.all() if self.keep_window == 0 else Retention.window(max(self.window, self.keep_window))
+            need = KVNeed(need.num_kv_heads, need.head_dim, keep)
+        return need
 
     @staticmethod
     def padded_size(head_dim: int, value_dim: int, dtype: torch.dtype) -> int:
@@ -255,15 +285,20 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
         k_col = Hq * dk
         v_col = k_col if self.values_are_keys else k_col + Hkv * dk  # the keys as projected stand in for values
         gate_col = v_col + (Hkv * dk if self.values_are_keys else Hkv * dv)
+        if not self.projects_kv:
+            if cache.writes:
+                raise RuntimeError("an attention layer without key and value projections was scheduled to fill a cache")
+            gate_col = k_col
         q = torch.empty((n, Hq, self.head_dim), dtype=ctx.runtime.dtype, device=out.device)
         with scope("rope"):
             K.rope_norm_kv_store(K.rows_view(proj.data, proj.splits, col), k_col, v_col, q,
                                  cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
                                  ctx.req_of_token, ctx.positions, self.q_norm_weight, self.k_norm_weight, self.eps,
-                                 self.inv_freq, self.rot_dims, Hq, Hkv, dk, dv, ctx.status, self.pairing, self.norm)
+                                 self.inv_freq, self.rot_dims, Hq, Hkv, dk, dv, ctx.status, self.pairing, self.norm,
+                                 self.rot_amplitude)
         attn = torch.empty_like(q)
         with scope("attention"):
-            self.attend(ctx, q, cache, attn, 0.0, 1.0)
+            self.attend(ctx, q, cache, attn, *self.q_temperature)
             gate = K.rows_view(proj.data, proj.splits, col + gate_col) if self.gated else None
             K.head_gate(attn, gate, mult, out, dv, per_channel=self.gate == "channel")
 

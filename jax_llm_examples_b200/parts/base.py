@@ -124,9 +124,22 @@ class Scaled:
         return zero
 
 
+@dataclasses.dataclass
+class StreamMixed:
+    """A sublayer output that is still to be written into several residual streams: x_t <- sum_s mix[s, t] x_s +
+    write[t] * rows, for all streams t at once.  Only a norm that knows the streams (``StreamRMSNorm``) can add it: it
+    does so in the same pass as the next sublayer's read and norm."""
+
+    rows: Rows
+    mix: torch.Tensor  # float32 [S, S], indexed [from, to]
+    write: torch.Tensor  # float32 [S]
+
+
 def as_rows(x: "torch.Tensor | Rows | RowSum | PostNormed | Scaled | None") -> "Rows | None":
     if x is None or isinstance(x, Rows):
         return x
+    if isinstance(x, StreamMixed):
+        raise TypeError("a sublayer output pending for several residual streams can only be added by a norm that keeps the streams")
     if isinstance(x, (RowSum, PostNormed, Scaled)):
         return Rows(x.materialize(), 1)
     return Rows(x, 1)

@@ -204,6 +204,48 @@ class EmbeddingReentryBlock(Block):
         return RowSum(terms + [Rows(x0, 1)], materialize)
 
 
+class HyperConnectionBlock(Block):
+    """A pre-norm block over several residual streams per token.  Each sublayer q (mixer, then feed-forward) has read
+    weights in_q [S], write weights out_q [S] and a mix matrix mix_q [S, S] (indexed [from, to]):
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t at once).
+
+    The read weights live in the norms (``StreamRMSNorm``); a sublayer's output goes on as a :class:`StreamMixed`, so
+    that its write-back, the next sublayer's read and that sublayer's norm are one kernel.  The feed-forward (with its
+    norm and weights) may be missing."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, mix1: torch.Tensor, write1: torch.Tensor, norm2: Norm | None = None,
+                 feed_forward: FeedForward | None = None, mix2: torch.Tensor | None = None, write2: torch.Tensor | None = None):
+        if len({feed_forward is None, norm2 is None, mix2 is None, write2 is None}) != 1:
+            raise ValueError("a feed-forward comes with its norm, its mix matrix and its write weights, or not at all")
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
+        self.mix1, self.write1, self.mix2, self.write2 = f32(mix1), f32(write1), f32(mix2), f32(write2)
+        S = self.write1.numel()
+        if self.mix1.shape != (S, S) or (self.mix2 is not None and (self.mix2.shape != (S, S) or self.write2.numel() != S)):
+            raise ValueError(f"{S} streams take mix matrices of {S} x {S} and {S} write weights")
+
+    def sub_parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache):
+        from .base import StreamMixed, as_rows
+
+        dt = ctx.runtime.dtype
+        with scope("attn_pre_norm"):
+            h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
+        y = self.mixer.forward(ctx, h, cache)
+        pending = StreamMixed(as_rows(y), self.mix1, self.write1)
+        if self.feed_forward is None:
+            return pending
+        with scope("attn_post_norm"):
+            h, h32, _ = self.norm2.forward(ctx, x, pending, out_dtype=dt, want_f32=self.feed_forward.needs_f32_input)
+        with scope("ffn"):
+            y = self.feed_forward.forward(ctx, h, h32, None)
+        return StreamMixed(as_rows(y), self.mix2, self.write2)
+
+
+register_part("block", "hyper_connection", HyperConnectionBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "reinjection", ReinjectionBlock)
 register_part("block", "embedding_reentry", EmbeddingReentryBlock)

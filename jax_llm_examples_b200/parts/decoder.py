@@ -41,8 +41,12 @@ class DecoderModel:
     """Embedding, scheduled blocks, final norm, LM head (llama4/llama4_jax/model.py:1186-1204)."""
 
     def __init__(self, runtime: Runtime, embedding: torch.Tensor, blocks: list[Block], final_norm: Norm,
-                 lm_head: torch.Tensor, schedule: list[LayerRun] | None = None, config=None, embedding_scale: float = 1.0):
+                 lm_head: torch.Tensor, schedule: list[LayerRun] | None = None, config=None, embedding_scale: float = 1.0,
+                 residual_streams: int | None = None):
         self.runtime, self.embedding, self.blocks = runtime, embedding, blocks
+        # None: one residual row per token.  A number S: every token carries S rows (x is [N, S * D]), all equal to
+        # the embedding's output at the start; the blocks' and the final norms are the kind that keeps streams.
+        self.residual_streams = residual_streams
         self.final_norm, self.lm_head, self.config = final_norm, lm_head, config
         self.embedding_scale = float(embedding_scale)  # the residual stream starts as scale * embedding row
         self.vocab_size, self.hidden_size = embedding.shape
@@ -95,8 +99,10 @@ class DecoderModel:
                     if (w.num_kv_heads, w.head_dim, w.planes) != (need.num_kv_heads, need.head_dim, need.planes):
                         raise ValueError(f"schedule entry {pos}: cache {run.cache} has other head sizes than this mixer")
                     if w.retention != need.retention:
-                        # the reader must not need keys that the writer's group gives back
-                        if w.retention != Retention.all():
+                        # the reader must not need keys that the writer's group gives back: the writer keeps everything,
+                        # or both look back over a window and the writer's is at least as long
+                        wide = w.retention.kind == need.retention.kind == Retention.window(1).kind and w.retention.size >= need.retention.size
+                        if w.retention != Retention.all() and not wide:
                             raise ValueError(f"schedule entry {pos}: reads a cache whose pages are released by another rule")
             needs = mixer.state_needs()
             if len(needs) != len(run.state_indices):
@@ -165,6 +171,10 @@ class DecoderModel:
         K.embed(ctx.token_ids, self.embedding, x, ctx.status, self.embedding_scale)
         if self.keeps_embedding_output:
             ctx.scratch["embedding_output"] = x.clone()
+        if self.residual_streams is not None:
+            # the first norm writes the streams from the embedding's rows while it reads them
+            ctx.scratch["streams_start"] = x
+            x = torch.empty((ctx.n_tokens, self.residual_streams * self.hidden_size), dtype=torch.float32, device=rt.device)
         delta = None
         for run in self.schedule:
             slabs = tuple(states[i] for i in run.state_indices)

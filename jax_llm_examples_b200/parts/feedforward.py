@@ -25,16 +25,21 @@ class DenseSwiGLU(FeedForward):
     kernel_libraries = ("elementwise", "gemm_simt")
     kernel_libraries_bf16 = ("gemm_stream",)
 
-    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, glu=K.SILU_GLU):
+        """``glu``: another form of the gated activation, ``K.glu_form(alpha, limit, shift)``:
+        g sigmoid(alpha g) (u + shift) with g = min(gate, limit) and u = clamp(up, -limit, limit)."""
         if w_gate_up.shape[0] != 2 * w_down.shape[1] or w_gate_up.shape[1] != w_down.shape[0]:
             raise ValueError(f"SwiGLU weights do not fit: gate_up {tuple(w_gate_up.shape)}, down {tuple(w_down.shape)}")
         self.interleaved = _can_interleave(w_gate_up)
         self.w_gate_up = interleave_gate_up(w_gate_up) if self.interleaved else w_gate_up
         self.w_down = w_down
+        self.glu = tuple(glu)
+
+    glu = K.SILU_GLU
 
     def forward(self, ctx: StepContext, h, h32=None, routing=None):
         with scope("gate_up_proj"):  # the reference's "gate" and "up_proj" (model.py:1145-1149) as one product
-            act = swiglu_linear(ctx, h, self.w_gate_up, self.interleaved, ctx.runtime.dtype)
+            act = swiglu_linear(ctx, h, self.w_gate_up, self.interleaved, ctx.runtime.dtype, self.glu)
         with scope("down_proj"):
             return linear(ctx, act, self.w_down, torch.float32, partials=True)
 
@@ -306,3 +311,97 @@ class SoftmaxRoutedMLPExperts(FeedForward):
 
 
 register_part("feed_forward", "softmax_routed_mlp", SoftmaxRoutedMLPExperts)
+
+
+class GroupLimitedGLUExperts(FeedForward):
+    """Gated experts chosen by a softmax router whose choice is corrected and limited to groups, their OUTPUTS weighted:
+
+        s = softmax(W_router h) over ALL router outputs (float32);  the choice is made on s + correction, among the
+        ``keep`` best of ``groups`` equal groups of neighbouring outputs (a group's score is its largest choice score);
+        weights = the chosen s / (their sum + 1e-20) * ``route_scale``;
+        out = sum_j weight_j * expert_j(h)  (+ shared(h): an expert that takes every token).
+
+    The last ``identity`` router outputs are experts without weights whose output is their input.  An expert is
+    down(act(gate h, up h)) with the gated activation ``glu`` (``K.glu_form``).  ``w_router``: [E + identity, D];
+    ``correction``: [E + identity] or None; ``we_gate_up``: [E, 2F, D] (gate rows then up rows); ``we_down``: [E, D, F].
+    The tokens' rows are gathered in expert order (unscaled; the identity experts' pairs sort behind the real ones and
+    no product sees them), both products run as grouped products, and the kernel that brings the rows back applies
+    the weights, puts the token's own row in an identity expert's place and adds the shared expert."""
+
+    kernel_libraries = ("moe", "elementwise", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
+    needs_f32_input = True
+    MANY_ROWS = 64  # above this many rows (bfloat16) the router shares each of its rows among eight tokens
+
+    def __init__(self, w_router: torch.Tensor, correction: torch.Tensor | None, we_gate_up: torch.Tensor, we_down: torch.Tensor,
+                 top_k: int, identity: int = 0, groups: int = 1, keep: int = 1, route_scale: float = 1.0, glu=K.SILU_GLU,
+                 shared: "DenseSwiGLU | None" = None):
+        E = we_gate_up.shape[0]
+        total = E + identity
+        if w_router.shape[0] != total or we_down.shape[0] != E or we_gate_up.shape[1] != 2 * we_down.shape[2] \
+                or we_gate_up.shape[2] != we_down.shape[1] or w_router.shape[1] != we_down.shape[1] \
+                or (correction is not None and correction.numel() != total):
+            raise ValueError(f"expert weights do not fit: router {tuple(w_router.shape)} for {E} experts + {identity} that hand their "
+                             f"input on, gate_up {tuple(we_gate_up.shape)}, down {tuple(we_down.shape)}")
+        if not 1 <= top_k <= total:
+            raise ValueError(f"top-{top_k} of {total} router outputs")
+        if groups < 1 or total % groups or not 1 <= keep <= groups or groups > K.ROUTER_MAX_GROUPS:
+            raise ValueError(f"{groups} groups (keep {keep}) do not divide {total} router outputs evenly")
+        self.w_router = w_router.to(torch.float32).contiguous()
+        self.correction = None if correction is None else correction.to(torch.float32).contiguous()
+        self.interleaved = _can_interleave(we_gate_up)
+        self.we_gate_up = interleave_gate_up(we_gate_up) if self.interleaved else we_gate_up.contiguous()
+        self.we_down = we_down.contiguous()
+        self.top_k, self.num_experts, self.identity, self.total = top_k, E, int(identity), total
+        self.groups, self.keep, self.route_scale, self.glu, self.shared = int(groups), int(keep), float(route_scale), tuple(glu), shared
+
+    def sub_parts(self):
+        return () if self.shared is None else (self.shared,)
+
+    def forward(self, ctx: StepContext, h, h32, routing=None):
+        rt = ctx.runtime
+        n, D = h32.shape
+        k, E, T, dev = self.top_k, self.num_experts, self.total, h32.device
+        topk_idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+        topk_w = torch.empty((n, k), dtype=torch.float32, device=dev)
+        K.router(h32, self.w_router, topk_idx, topk_w, many_rows=rt.dtype == torch.bfloat16 and n > self.MANY_ROWS,
+                 weight_form="softmax_normalized", correction=self.correction, groups=self.groups, keep=self.keep,
+                 scale=self.route_scale)
+        if "record_routing" in ctx.scratch:
+            ctx.scratch["record_routing"].append(topk_idx)
+        with scope("moe_routed_expert"):
+            with scope("permute"):
+                offsets = torch.empty(T + 1, dtype=torch.int32, device=dev)
+                sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
+                sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
+                tiles = None
+                if self.we_gate_up.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16:
+                    tile_rows = K.gemm_stream_token_tile(group_rows_hint(n * k, E))
+                    tiles = (torch.empty(2 * (-(-n * k // tile_rows) + T), dtype=torch.int32, device=dev),
+                             torch.empty(1, dtype=torch.int32, device=dev))
+                    K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, T, ctx.status, 0, tile_rows, *tiles, tile_groups=E)
+                else:
+                    K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, T, ctx.status)
+                a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=dev)
+                K.permute_scale(h32, sorted_pair, None, a_sorted, k)
+            # the grouped products see the first E groups only: offsets[0..E]
+            with scope("we_gate_up"):
+                one_product = grouped_swiglu_streams(a_sorted, self.we_gate_up, self.interleaved)
+                act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up, offsets, self.interleaved, rt.dtype, 0, tiles, self.glu)
+            with scope("we_down"):
+                y = as_rows(grouped_linear(ctx, act, self.we_down, offsets, torch.float32, partials=True, tiles=tiles,
+                                           after_grouped=one_product and not tracing_active()))
+        shared = None
+        if self.shared is not None:
+            with scope("moe_shared_expert"):
+                shared = as_rows(self.shared.forward(ctx, h, None))
+        delta = torch.empty((n, D), dtype=torch.float32, device=dev)
+        with scope("unpermute"):
+            ident = self.identity > 0
+            K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
+                          1 if shared is None else shared.splits, y.splits, -1, pair_weights=topk_w,
+                          topk_idx=topk_idx if ident else None, n_real=E, h_rows=h32 if ident else None)
+        return delta
+
+
+register_part("feed_forward", "group_limited_glu_experts", GroupLimitedGLUExperts)

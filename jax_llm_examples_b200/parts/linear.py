@@ -94,16 +94,18 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.
 
 
 def swiglu_linear(ctx: StepContext, a: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool,
-                  out_dtype: torch.dtype) -> torch.Tensor:
+                  out_dtype: torch.dtype, glu=K.SILU_GLU) -> torch.Tensor:
     """silu(a Wg^T) * (a Wu^T) for stacked [2F, K] weights: in the product's epilogue where the streaming
-    kernel runs and the rows are interleaved, else a product followed by the activation kernel."""
+    kernel runs and the rows are interleaved, else a product followed by the activation kernel.  ``glu``: another
+    form of the gated activation (``K.glu_form``).  The sums reach the activation in float32 unless the library's
+    bfloat16 product made them (many rows)."""
     M, F = a.shape[0], w_gate_up.shape[0] // 2
     act = torch.empty((M, F), dtype=out_dtype, device=a.device)
     if interleaved and _streams(a, w_gate_up, True):
-        K.gemm_stream(a, w_gate_up, act, ctx.status, mode=K.GEMM_SWIGLU)
+        K.gemm_stream(a, w_gate_up, act, ctx.status, mode=K.GEMM_SWIGLU, glu=glu)
         return act
     gu = linear(ctx, a, w_gate_up, out_dtype)
-    K.silu_mul(gu, act, interleaved=interleaved)
+    K.silu_mul(gu, act, interleaved=interleaved, glu=glu)
     return act
 
 
@@ -141,14 +143,14 @@ def grouped_swiglu_streams(a_sorted: torch.Tensor, w_gate_up: torch.Tensor, inte
 
 
 def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: torch.Tensor, offsets: torch.Tensor,
-                          interleaved: bool, out_dtype: torch.dtype, largest_group: int = 0, tiles=None) -> torch.Tensor:
+                          interleaved: bool, out_dtype: torch.dtype, largest_group: int = 0, tiles=None, glu=K.SILU_GLU) -> torch.Tensor:
     """``largest_group``: rows of a group known to be large (a shared expert's), so that one tile holds it."""
     rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
     act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
     if grouped_swiglu_streams(a_sorted, w_gate_up, interleaved):
         hint = _group_rows_hint(rows, E, largest_group)
-        K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU, tiles=tiles)
+        K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU, tiles=tiles, glu=glu)
         return act
     gu = grouped_linear(ctx, a_sorted, w_gate_up, offsets, out_dtype)
-    K.silu_mul(gu, act, interleaved=interleaved)
+    K.silu_mul(gu, act, interleaved=interleaved, glu=glu)
     return act

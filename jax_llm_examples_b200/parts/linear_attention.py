@@ -17,7 +17,7 @@ from .linear import grouped_linear, linear
 
 
 def _scan(ctx: StepContext, q, k, v, z, z_bias, form: str, tau: float, q_scale: float, bonus, state, heads: int, dk: int, dv: int,
-          read_after_update: bool) -> torch.Tensor:
+          read_after_update: bool, **prep) -> torch.Tensor:
     """The recurrence over the step's tokens from projected rows (views); returns o float32 [N, H, dv]."""
     n, dev = ctx.n_tokens, state.device
     need = n * heads * (3 * dk + 2 * dv)
@@ -34,7 +34,7 @@ def _scan(ctx: StepContext, q, k, v, z, z_bias, form: str, tau: float, q_scale: 
         return t
 
     qo, ko, do, vo, o = cut(n, heads, dk), cut(n, heads, dk), cut(n, heads, dk), cut(n, heads, dv), cut(n, heads, dv)
-    K.decay_prep(q, k, v, z, z_bias, form, tau, q_scale, qo, ko, do, vo, heads, dk, dv)
+    K.decay_prep(q, k, v, z, z_bias, form, tau, q_scale, qo, ko, do, vo, heads, dk, dv, **prep)
     K.decay_scan(qo, ko, do, vo, bonus, state, ctx.cu_q, ctx.slot_ids, o, read_after_update)
     return o
 
@@ -151,5 +151,47 @@ class TimeMixWKV(Mixer):
             return linear(ctx, out, self.w_o, torch.float32, partials=True)
 
 
+class RetentionMixer(ProjectedMixer):
+    """Linear attention with ONE fixed decay per head and neither softmax nor denominator:
+
+        q = W_q h, k = W_k h (H heads of dk), v = W_v h (H heads of dv); q and k turned by the token's position on their
+        first ``rot_dims`` entries (entry i with i + rot_dims / 2, angle position * inv_freq[i]); k times ``k_scale``;
+        S_t = decay_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t;
+        each head's o divided by its root mean square (no weight), times silu(W_g h), through W_o.
+
+    ``w_in``: [2 H dk + 2 H dv, D] = the q, k, v and gate projections stacked in that order; ``decay``: [H] numbers in
+    (0, 1].  State: float32 [H, dk, dv] per request, zero at the start.  The recurrence is the decay-scan kernel's with
+    a decay that is the same for every key channel of a head and every token."""
+
+    kernel_libraries = ("decay_scan", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
+
+    def __init__(self, w_in: torch.Tensor, w_o: torch.Tensor, decay: torch.Tensor, heads: int, dim: int, vdim: int, eps: float,
+                 k_scale: float = 1.0, q_scale: float = 1.0, inv_freq: torch.Tensor | None = None, rot_dims: int = 0):
+        if w_in.shape[0] != 2 * heads * (dim + vdim) or w_o.shape[1] != heads * vdim or w_o.shape[0] != w_in.shape[1] or decay.numel() != heads:
+            raise ValueError(f"retention weights do not fit {heads} heads of {dim} x {vdim}: w_in {tuple(w_in.shape)}, o {tuple(w_o.shape)}, "
+                             f"{decay.numel()} decays")
+        if rot_dims % 2 or not 0 <= rot_dims <= dim or (rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2)):
+            raise ValueError(f"{rot_dims} rotated entries of {dim} need {rot_dims // 2} frequencies")
+        self.w_in, self.w_o = w_in, w_o
+        self.decay = decay.to(torch.float32).contiguous()
+        self.inv_freq = None if inv_freq is None else inv_freq.to(torch.float32).contiguous()
+        self.heads, self.dim, self.vdim, self.eps = heads, dim, vdim, float(eps)
+        self.k_scale, self.q_scale, self.rot_dims = float(k_scale), float(q_scale), int(rot_dims)
+
+    def state_need(self):
+        return StateNeed((self.heads, self.dim, self.vdim), torch.float32)
+
+    def core(self, ctx: StepContext, h, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
+        H, dk, dv = self.heads, self.dim, self.vdim
+        view = lambda c: K.rows_view(proj.data, proj.splits, col + c)  # noqa: E731
+        with scope("attention"):
+            o = _scan(ctx, view(0), view(H * dk), view(2 * H * dk), None, None, "head_constant", 1.0, self.q_scale, None, cache.state,
+                      H, dk, dv, True, head_decay=self.decay, k_scale=self.k_scale, inv_freq=self.inv_freq, rot_dims=self.rot_dims,
+                      positions=ctx.positions)
+            K.head_norm_gate(o, None, False, view(2 * H * dk + H * dv), self.eps, mult, out)
+
+
+register_part("mixer", "retention", RetentionMixer)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "time_mix_wkv", TimeMixWKV)

@@ -117,3 +117,42 @@ def add_to_residual(x: torch.Tensor, delta, *, pre_weight=None, pre_groups: int 
 
 
 register_part("norm", "group_rms", GroupRMSNorm)
+
+
+class StreamRMSNorm(Norm):
+    """The norm in front of a sublayer of a model that keeps ``streams`` residual rows per token (x: float32
+    [N, streams * D]): the sublayer reads  u = sum_t read[t] x_t  (``read`` None: the plain sum, as the model's final
+    norm does) and this part returns  weight * u / sqrt(mean(u^2) + eps).  A pending :class:`StreamMixed` (the output
+    of the sublayer before, with its mix matrix and write weights) is written into the streams in the same kernel,
+    which is to several streams what the residual-add + norm kernel is to one."""
+
+    kernel_libraries = ("stream_mix",)
+
+    def __init__(self, weight: torch.Tensor | None, eps: float, streams: int, read: torch.Tensor | None = None):
+        if not 1 <= streams <= K.STREAMS_MAX:
+            raise ValueError(f"{streams} residual streams; 1..{K.STREAMS_MAX} are supported")
+        if read is not None and read.numel() != streams:
+            raise ValueError(f"the read weights have {read.numel()} entries for {streams} streams")
+        self.weight = None if weight is None else weight.to(torch.float32).contiguous()
+        self.read = None if read is None else read.to(torch.float32).contiguous()
+        self.eps, self.streams = float(eps), int(streams)
+
+    def forward(self, ctx: StepContext, x, delta, *, out_dtype, want_f32=False, row_index=None, router=None):
+        from .base import StreamMixed
+
+        if delta is not None and not isinstance(delta, StreamMixed):
+            raise TypeError("a norm over several residual streams adds sublayer outputs that come with their mix and write weights")
+        n = x.shape[0] if row_index is None else row_index.numel()
+        D = x.shape[1] // self.streams
+        out = None if out_dtype is None else torch.empty((n, D), dtype=out_dtype, device=x.device)
+        out32 = torch.empty((n, D), dtype=torch.float32, device=x.device) if want_f32 else None
+        first = ctx.scratch.pop("streams_start", None)  # the embedding's rows, while the streams are still unwritten
+        rows = None if delta is None else delta.rows
+        K.stream_mix_norm(x, self.streams, first=first, y=None if rows is None else rows.data, y_splits=1 if rows is None else rows.splits,
+                          mix=None if delta is None else delta.mix, write=None if delta is None else delta.write, read=self.read,
+                          gamma=self.weight, eps=self.eps, out=out, out32=out32, row_index=row_index,
+                          sum_out=ctx.scratch.get("stream_sum_probe"))
+        return out, out32, None
+
+
+register_part("norm", "stream_rms", StreamRMSNorm)

@@ -111,3 +111,22 @@ class UnfusedEncoding(PositionEncoding):
             K.kv_store(k.to(qkv.dtype).contiguous(), v.contiguous(), cache.pages, cache.block_table, ctx.req_of_token,
                        ctx.positions, ctx.status)
         return q.to(qkv.dtype).contiguous()
+
+
+def yarn_frequencies(base: float, dims: int, factor: float, original: float, fast: float, slow: float) -> "tuple[torch.Tensor, float]":
+    """(frequencies float32 [dims / 2], amplitude) of a rotation stretched to ``factor`` times the length ``original``
+    the YaRN way.  With f_i = base^(-2i / dims) and index(t) = dims ln(original / (2 pi t)) / (2 ln base), the pair
+    index whose wave makes t turns over the original length: lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)),
+    dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); the frequency is f_i / factor where ramp_i = 1
+    (slow waves), f_i where it is 0 (fast waves), the blend between.  cos and sin are both multiplied by the amplitude
+    0.1 ln(factor) + 1.  Evaluated in float64 and rounded once."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+
+    def index_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
