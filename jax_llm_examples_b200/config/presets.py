@@ -153,6 +153,53 @@ PRESETS["vofusun_tiny"] = {
     ],
     "loop": {"start": 1, "stop": 3, "times": 2},
 }
+def koduzen_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 32768, experts: int = 0, streams: int = 2) -> dict[str, Any]:
+    """A Koduzen configuration at the layer sizes of a real model, ``streams`` residual rows per token: biased attention
+    (head size 128, four query heads per key head, a window of 1024, a query temperature), a second such layer that reads
+    the first one's keys and values, retention (state 128 x 128 per head, half of each head rotated) and attention normed
+    over the whole projection with YaRN-scaled rotation in turn; a dense gated unit in every layer, or with ``experts``
+    > 0 a mixture (top 2 of the experts plus two that hand their input on, in groups of which half are kept; each expert
+    and the shared one a quarter of ``ff``) in every second layer."""
+    kv = max(heads // 4, 1)
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    groups = 2 if (experts + 2) % 2 == 0 else 1
+    routed = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0},
+              "router": {"experts": experts, "identity": 2, "top": 2, "scale": 1.0, "groups": {"count": groups, "keep": max(groups // 2, 1)}}}
+    biased = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5,
+              "q_temp": {"coef": 0.1, "every": 1024}}
+    kinds = [
+        lambda i: {"type": "attention_2", "mixer": dict(biased)},
+        lambda i: {"type": "attention_2", "mixer": dict(biased, kv_from=i - 1)},
+        lambda i: {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
+                                                  "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(heads - 1, 1)) for h in range(heads)]}},
+        lambda i: {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5,
+                                                  "rot": {"base": 500000.0, "dims": 128,
+                                                          "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}},
+    ]
+    cfg = {"architecture": "Koduzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+           "layers": [dict(kinds[i % 4](i), mlp=routed if experts and i % 2 else dense) for i in range(layers)]}
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+# Koduzen, tiny: three streams, a layer that reads its neighbour's keys, identity experts in groups, a layer without a feed-forward.
+PRESETS["koduzen_tiny"] = {
+    "architecture": "Koduzen", "vocab": 256, "width": 64, "norm": {"eps": 1e-6}, "streams": 3,
+    "layers": [
+        {"type": "attention_2", "mlp": {"kind": "dense", "ff": 96, "limit": 2.0},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "mask": {"size": 24}, "scale": 0.25, "q_temp": {"coef": 0.2, "every": 8}}},
+        {"type": "attention_2", "mlp": {"kind": "moe", "expert": {"ff": 32, "limit": 1.0}, "shared": {"ff": 16, "limit": 1.0},
+                                        "router": {"experts": 4, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 3, "keep": 2}}},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "mask": {"size": 40}, "scale": 0.2, "kv_from": 0}},
+        {"type": "retention", "mlp": None, "mixer": {"heads": 2, "dim": 8, "vdim": 16, "decay": [0.97, 0.995], "rot": {"base": 10000.0, "dims": 4}}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 64, "limit": 1.0},
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "mask": {"size": 33}, "scale": 0.2,
+                   "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}}},
+    ],
+}
+PRESETS["koduzen_2k"] = koduzen_sized(2048, 8, 16, 8192)
+PRESETS["koduzen_4k"] = koduzen_sized(4096, 8, 32, 14336)
 PRESETS["vofusun_2k"] = vofusun_sized(2048, 8, 16, 8192)
 PRESETS["vofusun_4k"] = vofusun_sized(4096, 8, 32, 14336)
 PRESETS["makisun_2k"] = makisun_sized(2048, 8, 16, 8192)

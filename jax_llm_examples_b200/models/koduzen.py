@@ -73,8 +73,8 @@ def tensor_specs(cfg: KoduzenConfig) -> dict[str, TensorSpec]:
                     specs += glu(p + "mlp.shared.", L.mlp.shared)
         if S is not None:
             for hc in ("hc1.",) + (("hc2.",) if L.mlp is not None else ()):
-                specs += [TensorSpec(p + hc + "in", (S,), "unit"), TensorSpec(p + hc + "out", (S,), "unit"),
-                          TensorSpec(p + hc + "mix", (S, S), "unit")]
+                specs += [TensorSpec(p + hc + "in", (S,), "norm"), TensorSpec(p + hc + "out", (S,), "norm"),
+                          TensorSpec(p + hc + "mix", (S, S), "identity")]
     specs.append(TensorSpec("final.norm", (D,), "norm"))
     return {s.name: s for s in specs}
 

@@ -27,7 +27,7 @@ import torch
 class TensorSpec:
     name: str
     shape: tuple[int, ...]  # an entry of -1: a size that only the stored tensor gives (any size fits)
-    init: str = "normal"  # "normal": N(0, std); "norm": 1 + N(0, norm_noise); "bias": N(0, 1/4); "unit": in (0, 1)
+    init: str = "normal"  # "normal": N(0, std); "norm": 1 + N(0, norm_noise); "bias": N(0, 1/4); "unit": in (0, 1); "identity": I + N(0, norm_noise)
     optional: bool = False
 
 

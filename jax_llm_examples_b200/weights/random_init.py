@@ -43,6 +43,8 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device: str |
             return torch.sigmoid(t).to(dtype)
         if spec.init == "bias":  # biases, per-channel filters, sinks: wide enough to matter
             return (0.5 * t).to(dtype)
+        if spec.init == "identity":  # a square matrix near the identity (a mix between residual streams)
+            return (torch.eye(spec.shape[0], device=device) + norm_noise * t).to(dtype)
         return (std * t).to(dtype)
     # large tensors: draw in the target precision, slab by slab, to bound the temporary
     out = torch.empty(spec.shape, dtype=dtype, device=device)

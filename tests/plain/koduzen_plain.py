@@ -199,7 +199,7 @@ def route(h, P, p, r):
     """(chosen [T, top], weights [T, top]) over experts and identity experts together."""
     z = h @ P[p + "router"].T
     s = torch.softmax(z, dim=-1)
-    choice = s + P[p + "correction"]
+    choice = s + P[p + "correction"] if (p + "correction") in P else s
     n = choice.shape[1]
     groups = r.get("groups")
     if groups:
@@ -210,19 +210,21 @@ def route(h, P, p, r):
         choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
     chosen = torch.topk(choice, r["top"], dim=-1).indices
     w = torch.gather(s, 1, chosen)
-    return chosen, w / (w.sum(-1, keepdim=True) + 1e-20) * r["scale"]
+    return chosen, w / (w.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
 
 
 def expert_mixture(h, P, p, ml, forced=None):
-    """``forced``: (chosen, weights-ignored) to take the choice from elsewhere (the weights are recomputed here)."""
+    """Returns (output, the experts used [T, top], the experts this router chose itself).  ``forced`` [T, top] replaces
+    the choice (the tests hand over the engine's, where two scores nearly tie); the weights are this router's."""
     r = ml["router"]
     real = r["experts"]
-    chosen, w = route(h, P, p, r)
+    own, w = route(h, P, p, r)
+    chosen = own
     if forced is not None:
-        chosen = forced
+        chosen = forced.to(torch.int64)
         s = torch.softmax(h @ P[p + "router"].T, dim=-1)
         w = torch.gather(s, 1, chosen)
-        w = w / (w.sum(-1, keepdim=True) + 1e-20) * r["scale"]
+        w = w / (w.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for c, wt in zip(chosen[t].tolist(), w[t]):
@@ -231,12 +233,12 @@ def expert_mixture(h, P, p, ml, forced=None):
             out[t] += wt * y[0]
     if ml.get("shared"):
         out = out + clipped_glu(h, P, p + "shared.", ml["shared"]["limit"])
-    return out, chosen
+    return out, chosen, own
 
 
 def feed_forward(h, P, p, ml, forced=None):
     if ml["kind"] == "dense":
-        return clipped_glu(h, P, p, ml["limit"]), None
+        return clipped_glu(h, P, p, ml["limit"]), None, None
     return expert_mixture(h, P, p, ml, forced)
 
 
@@ -250,9 +252,9 @@ def hyper_sublayer(X, P, p, fn):
 
 def forward(cfg: dict, P: dict, tokens, forced_choices=None, trace=None):
     """Logits [T, vocab] of one sequence.  ``forced_choices``: {layer: chosen [T, top]}; ``trace``: a list that gets
-    (the sum of the streams after every layer, the experts chosen per layer)."""
+    (the sum of the streams after the layer, the experts used, the experts its router chose itself) for every layer."""
     eps = cfg["norm"]["eps"]
-    S = cfg.get("streams", 1)
+    S = cfg.get("streams") or 1
     x = P["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     X = x[None].repeat(S, 1, 1)
     kvs = {}
@@ -269,14 +271,14 @@ def forward(cfg: dict, P: dict, tokens, forced_choices=None, trace=None):
                 kvs[i] = attention2_keys_values(h, P, p + "mix.", m)
             return attention2_mixer(h, P, p + "mix.", m, kvs[i if m.get("kv_from") is None else m["kv_from"]])
 
-        chosen = [None]
+        chosen = [None, None]
 
         def ff(u):
             h = rms_norm(u, P[p + "norm2"], eps)
-            y, chosen[0] = feed_forward(h, P, p + "mlp.", L["mlp"], None if forced_choices is None else forced_choices.get(i))
+            y, chosen[0], chosen[1] = feed_forward(h, P, p + "mlp.", L["mlp"], None if forced_choices is None else forced_choices.get(i))
             return y
 
-        if S > 1 or (p + "hc1.in") in P:
+        if (p + "hc1.in") in P:
             X = hyper_sublayer(X, P, p + "hc1.", mix)
             if L.get("mlp"):
                 X = hyper_sublayer(X, P, p + "hc2.", ff)
@@ -285,5 +287,5 @@ def forward(cfg: dict, P: dict, tokens, forced_choices=None, trace=None):
             if L.get("mlp"):
                 X = X + ff(X[0])[None]
         if trace is not None:
-            trace.append((X.sum(0), chosen[0]))
+            trace.append((X.sum(0), chosen[0], chosen[1]))
     return rms_norm(X.sum(0), P["final.norm"], eps) @ P["embed"].T
