@@ -477,12 +477,15 @@ def run_compare(args) -> dict:
     norm kernels) at equal width, depth, head count and feed-forward size, and Makisun with routed experts.
     --compare vofusun: the same for Vofusun beside Makisun (the closest: windowed attention over the same pages and a
     recurrence with a matrix state per head behind small per-token kernels) at equal width, depth, head count and
-    feed-forward size."""
+    feed-forward size.
+    --compare koduzen: the same for Koduzen beside Makisun (the closest: windowed attention over the same pages, a
+    recurrence on the same decay-scan kernel, routed experts whose outputs are weighted), both with a dense feed-forward
+    and with 16 routed experts in every second layer, at equal width, depth, head count and feed-forward size."""
     import torch
 
     import jax_llm_examples_b200 as J
     from jax_llm_examples_b200 import tracing
-    from jax_llm_examples_b200.config.presets import dense_llama_sized, makisun_sized, tebivik_sized, vofusun_sized
+    from jax_llm_examples_b200.config.presets import dense_llama_sized, koduzen_sized, makisun_sized, tebivik_sized, vofusun_sized
 
     peaks, peak_src = _peaks()
     hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
@@ -493,7 +496,7 @@ def run_compare(args) -> dict:
     if args.layers:
         sizes = [(w, args.layers, h, f) for w, _, h, f in sizes]
     what = {"tebivik": "Tebivik beside a dense Llama-4-style decoder", "makisun": "Makisun beside Tebivik",
-            "vofusun": "Vofusun beside Makisun"}[args.compare]
+            "vofusun": "Vofusun beside Makisun", "koduzen": "Koduzen beside Makisun"}[args.compare]
     out = {"metric": "prefill and decode throughput, " + what, "unit": "tok/s", "n_gpus": 1,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": peaks, "peaks_source": peak_src,
            "config": {"prefill_tokens": P, "decode_batch": B, "decode_context": C, "l2": "a 256 MiB buffer is written between timed steps"},
@@ -602,6 +605,62 @@ def run_compare(args) -> dict:
         }
         out["sizes"].append({"width": width, "layers": layers, "heads": heads, "ff": ff, "vofusun": v, "makisun": m,
                              "fraction_of_measured_roofline": roof})
+    for width, layers, heads, ff in sizes if args.compare == "koduzen" else ():
+        k, m = measure(koduzen_sized(width, layers, heads, ff)), measure(makisun_sized(width, layers, heads, ff))
+        kx, mx = measure(koduzen_sized(width, layers, heads, ff, experts=16)), measure(makisun_sized(width, layers, heads, ff, experts=16))
+        # Koduzen's layers in turn: biased attention, a reader of its pages, retention, normed attention; Makisun's:
+        # attention beside gated linear attention (half the heads), time mix
+        n_ret = sum(1 for i in range(layers) if i % 4 == 2)
+        n_att, n_own = layers - n_ret, sum(1 for i in range(layers) if i % 4 in (0, 3))
+        par, rec = (layers + 1) // 2, layers // 2
+        dh, hkv, window, S = 128, max(heads // 4, 1), 1024, 2
+        state = 128 * 128 * 8  # a head's state read and written, float32
+        m_heads = rec * heads + par * max(heads // 2, 1)
+        rows = 128 * 5 * 4  # q, k, decay, v in and o out per token and head
+        seen = sum(min(i + 1, window) for i in range(P))
+        keys = min(C, window)
+        norm_k = (2 * S * 4 + 4 + 2) * width  # streams read and written, the sublayer's output read, the normed row written
+        vk = lambda d, name: d.get(name, 0)  # noqa: E731
+        moe_layers = layers // 2
+        fe = ff // 4
+        # an expert layer's own kernels: router + sort + gather + combine move each token's row about (2 + 2 top) times
+        roof = {
+            "decode": {
+                "koduzen decay_scan": frac(vk(k["decode_kernels_ms"], "jlx_decay_scan"), n_ret * B * heads * (state + rows)),
+                "makisun decay_scan": frac(vk(m["decode_kernels_ms"], "jlx_decay_scan"), B * m_heads * (state + rows)),
+                "koduzen attention_decode": frac(vk(k["decode_kernels_ms"], "jlx_attention_decode"), n_att * B * keys * 2 * hkv * dh * 2),
+                "makisun attention_decode": frac(vk(m["decode_kernels_ms"], "jlx_attention_decode"), par * B * keys * 2 * hkv * dh * 2),
+                "koduzen stream_mix_norm": frac(vk(k["decode_kernels_ms"], "jlx_stream_mix_norm"), (2 * layers + 1) * B * norm_k),
+                "makisun group_norm": frac(vk(m["decode_kernels_ms"], "jlx_group_norm"), (2 * layers + 1) * B * width * 14),
+                "koduzen experts moe_combine": frac(vk(kx["decode_kernels_ms"], "jlx_moe_combine"), moe_layers * B * width * 4 * 5),
+                "makisun experts moe_combine": frac(vk(mx["decode_kernels_ms"], "jlx_moe_combine"), moe_layers * B * width * 4 * 5),
+            },
+            "prefill": {
+                "koduzen decay_scan": frac(vk(k["prefill_kernels_ms"], "jlx_decay_scan"), n_ret * P * heads * rows),
+                "makisun decay_scan": frac(vk(m["prefill_kernels_ms"], "jlx_decay_scan"), P * m_heads * rows),
+                "koduzen attention_prefill_tc": frac(vk(k["prefill_kernels_ms"], "jlx_attention_prefill_tc"), 0, n_att * heads * seen * 4 * dh),
+                "makisun attention_prefill_tc": frac(vk(m["prefill_kernels_ms"], "jlx_attention_prefill_tc"), 0, par * heads * seen * 4 * dh),
+                "koduzen stream_mix_norm": frac(vk(k["prefill_kernels_ms"], "jlx_stream_mix_norm"), (2 * layers + 1) * P * norm_k),
+                "makisun group_norm": frac(vk(m["prefill_kernels_ms"], "jlx_group_norm"), (2 * layers + 1) * P * width * 14),
+                "koduzen rope_half_kv_store": frac(vk(k["prefill_kernels_ms"], "jlx_rope_half_kv_store"),
+                                                   P * (n_own * (heads + 2 * hkv) + (n_att - n_own) * heads) * dh * 6),
+                "makisun rope_half_kv_store": frac(vk(m["prefill_kernels_ms"], "jlx_rope_half_kv_store"), P * par * (heads + 2 * hkv) * dh * 6),
+                "koduzen decay_prep": frac(vk(k["prefill_kernels_ms"], "jlx_decay_prep"), n_ret * P * heads * 128 * 7 * 4),
+                "makisun decay_prep": frac(vk(m["prefill_kernels_ms"], "jlx_decay_prep"), P * m_heads * 128 * 8 * 4),
+                "koduzen experts router": frac(vk(kx["prefill_kernels_ms"], "jlx_router"), moe_layers * P * width * 4),
+                "makisun experts router": frac(vk(mx["prefill_kernels_ms"], "jlx_router"), moe_layers * P * width * 4),
+                "koduzen experts moe_combine": frac(vk(kx["prefill_kernels_ms"], "jlx_moe_combine"), moe_layers * P * width * 4 * 5),
+                "makisun experts moe_combine": frac(vk(mx["prefill_kernels_ms"], "jlx_moe_combine"), moe_layers * P * width * 4 * 5),
+                "koduzen experts gemm_stream": frac(vk(kx["prefill_kernels_ms"], "jlx_gemm_stream"), 0, moe_layers * P * 2 * 3 * width * fe * 2),
+                "makisun experts gemm_stream": frac(vk(mx["prefill_kernels_ms"], "jlx_gemm_stream"), 0, moe_layers * P * 2 * 2 * width * fe * 2),
+            },
+            "scan_ns_per_token_and_layer": {
+                "koduzen decay_scan": round(vk(k["prefill_kernels_ms"], "jlx_decay_scan") * 1e6 / (P * max(n_ret, 1)), 1),
+                "makisun decay_scan": round(vk(m["prefill_kernels_ms"], "jlx_decay_scan") * 1e6 / (P * layers), 1),
+            },
+        }
+        out["sizes"].append({"width": width, "layers": layers, "heads": heads, "ff": ff, "koduzen": k, "makisun": m,
+                             "koduzen_16_experts": kx, "makisun_16_experts": mx, "fraction_of_measured_roofline": roof})
     for width, layers, heads, ff in sizes if args.compare == "makisun" else ():
         m, t = measure(makisun_sized(width, layers, heads, ff)), measure(tebivik_sized(width, layers, heads, ff))
         routed = measure(makisun_sized(width, layers, heads, ff, experts=16))
@@ -685,7 +744,7 @@ def main() -> int:
     ap.add_argument("--long-tokens", type=int, default=32768)
     ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
-    ap.add_argument("--compare", default=None, choices=["tebivik", "makisun", "vofusun"],
+    ap.add_argument("--compare", default=None, choices=["tebivik", "makisun", "vofusun", "koduzen"],
                     help="instead of the benchmark: throughput of this architecture at real layer sizes beside the closest "
                     "model the framework had before (with --prefill-tokens, --batch, --context up to 4096, --layers)")
     args = ap.parse_args()

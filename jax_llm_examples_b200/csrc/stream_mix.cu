@@ -13,7 +13,7 @@
 // depend on the batch.
 #include "common.cuh"
 
-#define STREAMS_MAX 8
+#define STREAMS_MAX 16
 
 struct StreamMixArgs {
   float* x;               // [N, S, D] streams, updated in place (not written when rows are gathered)
@@ -31,13 +31,32 @@ struct StreamMixArgs {
   int S, D;
 };
 
-template <typename T>
-__global__ void stream_mix_norm_kernel(StreamMixArgs a, T* __restrict__ out, float* __restrict__ out32) {
+// V consecutive channels of a row as one access (V = 4 needs D % 4 == 0 and 16-byte aligned rows).
+template <int V> struct Chan { float v[V]; };
+template <int V> __device__ __forceinline__ Chan<V> load_chan(const float* p) {
+  Chan<V> c;
+  if (V == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    c.v[0] = t.x; c.v[1 % V] = t.y; c.v[2 % V] = t.z; c.v[3 % V] = t.w;
+  } else {
+    c.v[0] = *p;
+  }
+  return c;
+}
+template <int V> __device__ __forceinline__ void store_chan(float* p, const Chan<V>& c) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(c.v[0], c.v[1 % V], c.v[2 % V], c.v[3 % V]);
+  else *p = c.v[0];
+}
+
+// MAXS: the stream count rounded up to 2, 4, 8 or 16 (a token's rows of V channels live in registers).  A channel's
+// sums run in the same order for V = 1 and V = 4.
+template <typename T, int MAXS, int V>
+__global__ void __launch_bounds__(512) stream_mix_norm_kernel(StreamMixArgs a, T* __restrict__ out, float* __restrict__ out32) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
-  extern __shared__ float u_row[];  // [D]
+  extern __shared__ __align__(16) float u_row[];  // [D]
   __shared__ float scratch[33];
-  __shared__ float w_mix[STREAMS_MAX * STREAMS_MAX], w_out[STREAMS_MAX], w_in[STREAMS_MAX];
+  __shared__ float w_mix[MAXS * MAXS], w_out[MAXS], w_in[MAXS];
   const int S = a.S, D = a.D;
   // the small weights are the model's: read before the wait
   for (int i = threadIdx.x; i < S * S; i += blockDim.x) w_mix[i] = a.y ? a.mix[i] : 0.f;
@@ -51,46 +70,61 @@ __global__ void stream_mix_norm_kernel(StreamMixArgs a, T* __restrict__ out, flo
   const size_t r = a.row_index ? (size_t)a.row_index[n] : n;
   float* xr = a.x + r * (size_t)S * D;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float xs[STREAMS_MAX];
+  for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+    Chan<V> xs[MAXS];
     if (a.x_first) {
-      const float v = a.x_first[r * D + d];
+      const Chan<V> c = load_chan<V>(a.x_first + r * D + d);
 #pragma unroll
-      for (int s = 0; s < STREAMS_MAX; ++s) xs[s] = v;
+      for (int s = 0; s < MAXS; ++s) xs[s] = c;
     } else {
 #pragma unroll
-      for (int s = 0; s < STREAMS_MAX; ++s) xs[s] = s < S ? xr[(size_t)s * D + d] : 0.f;
+      for (int s = 0; s < MAXS; ++s)
+        if (s < S) xs[s] = load_chan<V>(xr + (size_t)s * D + d);
     }
-    float u = 0.f, total = 0.f;
+    Chan<V> u, total, y;
+#pragma unroll
+    for (int i = 0; i < V; ++i) u.v[i] = total.v[i] = y.v[i] = 0.f;
     if (a.y) {
-      float y = 0.f;
-      for (int z = 0; z < a.y_splits; ++z) y += a.y[(size_t)z * a.y_stride + r * D + d];
+      for (int z = 0; z < a.y_splits; ++z) {
+        const Chan<V> c = load_chan<V>(a.y + (size_t)z * a.y_stride + r * D + d);
 #pragma unroll
-      for (int t = 0; t < STREAMS_MAX; ++t) {
+        for (int i = 0; i < V; ++i) y.v[i] += c.v[i];
+      }
+#pragma unroll
+      for (int t = 0; t < MAXS; ++t) {
         if (t < S) {
-          float v = 0.f;
+          Chan<V> v;
 #pragma unroll
-          for (int s = 0; s < STREAMS_MAX; ++s)
-            if (s < S) v = fmaf(w_mix[s * S + t], xs[s], v);
-          v = fmaf(w_out[t], y, v);
-          if (!a.row_index) xr[(size_t)t * D + d] = v;
-          u = fmaf(w_in[t], v, u);
-          total += v;
+          for (int i = 0; i < V; ++i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s)
+              if (s < S) acc = fmaf(w_mix[s * S + t], xs[s].v[i], acc);
+            acc = fmaf(w_out[t], y.v[i], acc);
+            v.v[i] = acc;
+            u.v[i] = fmaf(w_in[t], acc, u.v[i]);
+            total.v[i] += acc;
+          }
+          if (!a.row_index) store_chan<V>(xr + (size_t)t * D + d, v);
         }
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < STREAMS_MAX; ++t) {
+      for (int t = 0; t < MAXS; ++t) {
         if (t < S) {
-          if (a.x_first && !a.row_index) xr[(size_t)t * D + d] = xs[t];
-          u = fmaf(w_in[t], xs[t], u);
-          total += xs[t];
+          if (a.x_first && !a.row_index) store_chan<V>(xr + (size_t)t * D + d, xs[t]);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            u.v[i] = fmaf(w_in[t], xs[t].v[i], u.v[i]);
+            total.v[i] += xs[t].v[i];
+          }
         }
       }
     }
-    if (a.sum_out) a.sum_out[n * D + d] = total;
-    u_row[d] = u;
-    ss = fmaf(u, u, ss);
+    if (a.sum_out) store_chan<V>(a.sum_out + n * D + d, total);
+    store_chan<V>(u_row + d, u);
+#pragma unroll
+    for (int i = 0; i < V; ++i) ss = fmaf(u.v[i], u.v[i], ss);
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)D + a.eps);
@@ -116,12 +150,23 @@ JLX_API int jlx_stream_mix_norm(float* x, const float* x_first, const float* y, 
   StreamMixArgs a;
   a.x = x; a.x_first = x_first; a.y = y; a.y_stride = y_stride; a.y_splits = y_splits; a.mix = mix; a.out_w = out_w; a.in_w = in_w;
   a.gamma = gamma; a.eps = eps; a.row_index = row_index; a.sum_out = sum_out; a.S = S; a.D = D;
-  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
-  JLX_DISPATCH_DTYPE(out_dtype, T, {
-    if (smem > 48 * 1024)
-      JLX_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    JLX_CUDA(jlx_launch_pdl(stream_mix_norm_kernel<T>, dim3(n), dim3(threads), smem, stream, a, (T*)out, out32));
-  });
+  const int threads = D >= 4096 ? 512 : (D >= 1024 ? 256 : 128);
+  // four channels per access where every row starts on a 16-byte boundary
+  const bool wide = D % 4 == 0 && y_stride % 4 == 0 &&
+                    (((uintptr_t)x | (uintptr_t)x_first | (uintptr_t)y | (uintptr_t)sum_out) & 15) == 0;
+#define JLX_STREAMS_V(MAXS, V)                                                                                                       \
+  JLX_DISPATCH_DTYPE(out_dtype, T, {                                                                                                \
+    if (smem > 48 * 1024)                                                                                                           \
+      JLX_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<T, MAXS, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    JLX_CUDA(jlx_launch_pdl(stream_mix_norm_kernel<T, MAXS, V>, dim3(n), dim3(threads), smem, stream, a, (T*)out, out32));          \
+  })
+#define JLX_STREAMS(MAXS) do { if (wide) { JLX_STREAMS_V(MAXS, 4); } else { JLX_STREAMS_V(MAXS, 1); } } while (0)
+  if (S <= 2) JLX_STREAMS(2);
+  else if (S <= 4) JLX_STREAMS(4);
+  else if (S <= 8) JLX_STREAMS(8);
+  else JLX_STREAMS_V(16, 1);
+#undef JLX_STREAMS
+#undef JLX_STREAMS_V
   JLX_LAUNCH_CHECK("stream_mix_norm");
   return 0;
 }

@@ -216,7 +216,7 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: 
 
 
 # ------------------------------------------------------------------- several residual streams per token
-STREAMS_MAX = 8  # csrc/stream_mix.cu
+STREAMS_MAX = 16  # csrc/stream_mix.cu
 
 
 def stream_mix_norm(x: torch.Tensor, streams: int, *, first: torch.Tensor | None = None, y: torch.Tensor | None = None,

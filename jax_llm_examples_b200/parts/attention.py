@@ -279,17 +279,15 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
     def sub_parts(self):
         return ()
 
-    def core(self, ctx: StepContext, h, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
+    def _attend_rows(self, ctx: StepContext, proj: Rows, col: int, cache: LayerCache) -> torch.Tensor:
+        """Norm, rotation and page write of the projected rows, then attention: [N, Hq, padded size]."""
         Hq, Hkv, dk, dv = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
         n = proj.data.shape[-2]
         k_col = Hq * dk
         v_col = k_col if self.values_are_keys else k_col + Hkv * dk  # the keys as projected stand in for values
-        gate_col = v_col + (Hkv * dk if self.values_are_keys else Hkv * dv)
-        if not self.projects_kv:
-            if cache.writes:
-                raise RuntimeError("an attention layer without key and value projections was scheduled to fill a cache")
-            gate_col = k_col
-        q = torch.empty((n, Hq, self.head_dim), dtype=ctx.runtime.dtype, device=out.device)
+        if not self.projects_kv and cache.writes:
+            raise RuntimeError("an attention layer without key and value projections was scheduled to fill a cache")
+        q = torch.empty((n, Hq, self.head_dim), dtype=ctx.runtime.dtype, device=proj.data.device)
         with scope("rope"):
             K.rope_norm_kv_store(K.rows_view(proj.data, proj.splits, col), k_col, v_col, q,
                                  cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
@@ -299,11 +297,29 @@ class GatedPagedAttention(ProjectedMixer, PagedAttention):
         attn = torch.empty_like(q)
         with scope("attention"):
             self.attend(ctx, q, cache, attn, *self.q_temperature)
+        return attn
+
+    def core(self, ctx: StepContext, h, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
+        Hq, Hkv, dk, dv = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
+        gate_col = Hq * dk
+        if self.projects_kv:
+            gate_col += Hkv * dk + (0 if self.values_are_keys else Hkv * dv)
+        attn = self._attend_rows(ctx, proj, col, cache)
+        with scope("attention"):
             gate = K.rows_view(proj.data, proj.splits, col + gate_col) if self.gated else None
             K.head_gate(attn, gate, mult, out, dv, per_channel=self.gate == "channel")
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache):
-        return ProjectedMixer.forward(self, ctx, h, cache)
+        if self.gated or self.value_dim != self.head_dim:
+            return ProjectedMixer.forward(self, ctx, h, cache)
+        # no gate and no padding: the heads' outputs are the output product's rows as they lie
+        from .base import as_rows
+
+        with scope("qkv_matmul"):
+            proj = as_rows(linear(ctx, h, self.w_in, torch.float32, partials=True))
+        attn = self._attend_rows(ctx, proj, 0, cache)
+        with scope("projection"):
+            return linear(ctx, attn.view(attn.shape[0], -1), self.w_o, torch.float32, partials=True)
 
 
 register_part("mixer", "gated_paged_attention", GatedPagedAttention)
