@@ -37,10 +37,15 @@ struct RouterChoice {
 __device__ __forceinline__ void choose_experts(float* sc, int E, int k, int* __restrict__ idx, float* __restrict__ w, int weight_form,
                                                const RouterChoice& ch) {
   if (weight_form == 2) {
+    // the shares once (E exponentials), in place; after that the choice only compares and adds
     float m = -INFINITY, sum = 0.f;
     for (int e = 0; e < E; ++e) m = fmaxf(m, sc[e]);
-    for (int e = 0; e < E; ++e) sum += expf(sc[e] - m);
-    // sc[e] <- the choice score; the share s is recomputed for the chosen from the logit kept in w's place below
+    for (int e = 0; e < E; ++e) {
+      const float x = expf(sc[e] - m);
+      sc[e] = x;
+      sum += x;
+    }
+    for (int e = 0; e < E; ++e) sc[e] = sc[e] / sum;
     const int per = ch.groups > 1 ? E / ch.groups : E;
     unsigned long long allowed = ~0ull;  // bit g: group g may be chosen from (up to 64 groups)
     if (ch.groups > 1 && ch.keep < ch.groups) {
@@ -51,7 +56,7 @@ __device__ __forceinline__ void choose_experts(float* sc, int E, int k, int* __r
         for (int g = 0; g < ch.groups; ++g) {
           if ((allowed >> g) & 1ull) continue;
           float gv = -INFINITY;
-          for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, expf(sc[e] - m) / sum + (ch.correction ? ch.correction[e] : 0.f));
+          for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, sc[e] + (ch.correction ? ch.correction[e] : 0.f));
           if (bg < 0 || gv > bv) {
             bg = g;
             bv = gv;
@@ -60,28 +65,27 @@ __device__ __forceinline__ void choose_experts(float* sc, int E, int k, int* __r
         allowed |= 1ull << bg;
       }
     }
+    unsigned long long taken[ROUTER_MAX_E / 64] = {0ull, 0ull, 0ull, 0ull};
     float total = 0.f;
     for (int j = 0; j < k; ++j) {
       int best = -1;
-      float bv = 0.f, bs = 0.f;
+      float bv = 0.f;
       for (int e = 0; e < E; ++e) {
-        if (isnan(sc[e]) || !((allowed >> (ch.groups > 1 ? e / per : 0)) & 1ull)) continue;
-        const float share = expf(sc[e] - m) / sum;
-        const float v = share + (ch.correction ? ch.correction[e] : 0.f);
-        if (best < 0 || v > bv) {
+        if (((taken[e >> 6] >> (e & 63)) & 1ull) || !((allowed >> (ch.groups > 1 ? e / per : 0)) & 1ull)) continue;
+        const float v = sc[e] + (ch.correction ? ch.correction[e] : 0.f);
+        if (isnan(v)) continue;
+        if (best < 0 || v > bv) {  // strict: the lower index wins a tie
           best = e;
           bv = v;
-          bs = share;
         }
       }
-      if (best < 0) {  // fewer allowed outputs than k, or all NaN: still a valid index
-        best = j;
-        bs = 0.f;
-      }
+      float bs = 0.f;
+      if (best < 0) best = j;  // fewer allowed outputs than k, or all NaN: still a valid index, with no weight
+      else bs = sc[best];
       idx[j] = best;
       w[j] = bs;
       total += bs;
-      sc[best] = NAN;  // taken
+      taken[best >> 6] |= 1ull << (best & 63);
     }
     for (int j = 0; j < k; ++j) w[j] = w[j] / (total + 1e-20f) * ch.scale;
     return;
