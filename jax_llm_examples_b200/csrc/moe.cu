@@ -117,10 +117,23 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
   const int n = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const float* hr = h + (size_t)n * D;
+  // The newest weight form reads four columns per access with four sums under way (the walk below is a chain of
+  // loads that wait on one another); the older forms keep the order of their sums.
+  const bool wide = weight_form == 2 && (D & 3) == 0 && (((uintptr_t)h | (uintptr_t)w_router) & 15) == 0;
   for (int e = warp; e < E; e += nwarp) {
     const float* wr = w_router + (size_t)e * D;
     float s = 0.f;
-    for (int d = lane; d < D; d += 32) s = fmaf(hr[d], wr[d], s);
+    if (wide) {
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int d = lane * 4; d < D; d += 128) {
+        const float4 a = *reinterpret_cast<const float4*>(hr + d), b = *reinterpret_cast<const float4*>(wr + d);
+        s4[0] = fmaf(a.x, b.x, s4[0]); s4[1] = fmaf(a.y, b.y, s4[1]); s4[2] = fmaf(a.z, b.z, s4[2]); s4[3] = fmaf(a.w, b.w, s4[3]);
+      }
+      s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    } else {
+      for (int d = lane; d < D; d += 32) s = fmaf(hr[d], wr[d], s);
+    }
     s = warp_sum(s);
     if (lane == 0) scores[e] = bias ? s + bias[e] : s;
   }

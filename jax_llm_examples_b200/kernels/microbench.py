@@ -205,6 +205,23 @@ def conv_unit_prep(a) -> dict:
             "taps": taps, "us": round(t * 1e6, 1), "bytes": moved, "GB/s": round(moved / t / 1e9, 1)}
 
 
+def stream_mix_norm(a) -> dict:
+    """The kernel between two sublayers of a model with several residual rows per token: write-back with mixing, the next
+    read and its norm, for ``tokens`` rows of ``streams`` x ``width``."""
+    from . import api as K
+
+    N, S, D = a.tokens, a.streams, a.width
+    x = torch.randn(N, S * D, device="cuda")
+    y = torch.randn(a.splits, N, D, device="cuda")
+    mix, write, read, gamma = torch.randn(S, S, device="cuda"), torch.randn(S, device="cuda"), torch.randn(S, device="cuda"), torch.randn(D, device="cuda")
+    out = torch.empty(N, D, device="cuda", dtype=torch.bfloat16)
+    t = _time(lambda: K.stream_mix_norm(x, S, y=y, y_splits=a.splits, mix=mix, write=write, read=read, gamma=gamma, eps=1e-6, out=out),
+              a.reps, _flush(a))
+    moved = N * D * (8 * S + 4 * a.splits + 2)  # the rows read and written, the partials read, the normed row written
+    return {"kernel": "stream_mix_norm", "tokens": N, "streams": S, "width": D, "splits": a.splits, "us": round(t * 1e6, 1), "bytes": moved,
+            "GB/s": round(moved / t / 1e9, 1)}
+
+
 def _flush(a):
     return None if a.no_flush else torch.empty(256 * 1024 * 1024 // 4, device="cuda")
 
@@ -212,12 +229,17 @@ def _flush(a):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan", "delta_scan", "conv_unit_prep"):
+    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan", "delta_scan", "conv_unit_prep", "stream_mix_norm"):
         p = sub.add_parser(name)
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
         if name == "conv_unit_prep":
             p.add_argument("--taps", type=int, default=4)
+        if name == "stream_mix_norm":
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--streams", type=int, default=2)
+            p.add_argument("--width", type=int, default=4096)
+            p.add_argument("--splits", type=int, default=1)
         if name in ("delta_scan", "conv_unit_prep"):
             p.add_argument("--key-heads", type=int, default=0, help="heads of q and k (0: as many as value heads)")
         if name == "delta_scan":
@@ -253,7 +275,7 @@ def main(argv=None) -> int:
             p.add_argument("--swiglu", action="store_true", help="fused SiLU(gate) * up epilogue")
     a = ap.parse_args(argv)
     print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "decay_scan": decay_scan,
-                      "delta_scan": delta_scan, "conv_unit_prep": conv_unit_prep}[a.what](a)))
+                      "delta_scan": delta_scan, "conv_unit_prep": conv_unit_prep, "stream_mix_norm": stream_mix_norm}[a.what](a)))
     return 0
 
 
