@@ -517,6 +517,24 @@ def test_every_kind_of_cut_against_the_plain_implementation(folders, name, dtype
         assert engine.manager.free_slots() == 4 and all(engine.manager.free_pages(g) == engine.num_pages for g in range(len(engine.manager.groups)))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_size_128_on_pages_of_64_tokens(folders, dtype):
+    """Pages of 64 tokens, as a server has them: in bfloat16 the portions of 64 tokens and more of the layers with head
+    size 128 run on the tcgen05 kernel (with the distance bias, the sink, the temperature, and a reader of another
+    layer's pages), shorter ones on the mma.sync kernel, single tokens on the split-KV kernel, all in one step."""
+    name = "wide"
+    vocab = KH.config(name)["vocab"]
+    rng = random.Random(13)
+    requests = H.random_requests(rng, vocab, [200, 70, 131, 3])
+    engine = _engine(folders[name], dtype, max_tokens=12 * 64, page_size=64)
+    for steps in (H.trace_whole(requests), H.trace_tail_decode(requests, tail=20), H.trace_portions(requests, rng),
+                  H.trace_mixed(requests, rng, max_live=4)):
+        got, routing = H.run_trace(engine, steps, record_routing=True)
+        KH.compare(folders[name], requests, got, routing, dtype, stray=2 if dtype == "bfloat16" else 0)
+    if dtype == "bfloat16":
+        assert any("tc" in kinds for kinds in engine.attention_kernels_seen), "the tcgen05 kernel did not run"
+
+
 @pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5, 7, 8, 9, 10])
 def test_configurations_drawn_at_random_under_every_kind_of_cut(seed, tmp_path):
     """Sizes, head counts, orders of layers, windows, rotations, routers and stream counts that nobody chose, in both
