@@ -173,8 +173,8 @@ def koduzen_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 327
         lambda i: {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
                                                   "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(heads - 1, 1)) for h in range(heads)]}},
         lambda i: {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5,
-                                                  "rot": {"base": 500000.0, "dims": 128,
-                                                          "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}},
+                                                  "rot": {"base": 250000.0, "dims": 128,
+                                                          "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}},
     ]
     cfg = {"architecture": "Koduzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
            "layers": [dict(kinds[i % 4](i), mlp=routed if experts and i % 2 else dense) for i in range(layers)]}

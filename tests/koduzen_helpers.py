@@ -131,7 +131,7 @@ def random_config(rng) -> dict:
         base = rng.choice([100.0, 10000.0, 500000.0])
         if not scaling_ok:
             return (base, dims)
-        scaling = None if rng.random() < 0.4 else (rng.choice([2.0, 8.0]), rng.choice([16, 64, 1024]), rng.choice([8.0, 32.0]), rng.choice([1.0, 2.0]))
+        scaling = None if rng.random() < 0.4 else (rng.choice([2.0, 4.0]), rng.choice([16, 64, 512]), rng.choice([8.0, 16.0]), rng.choice([1.0, 2.0]))
         return (base, dims, scaling)
 
     layers = []
