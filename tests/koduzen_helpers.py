@@ -165,6 +165,60 @@ def random_config(rng) -> dict:
     return cfg
 
 
+def mid_size_config(rng) -> dict:
+    """A configuration drawn at random at sizes between the tiny ones above and a real model's: widths of 192 to 512, head
+    sizes 32 to 128 (96 is padded to 128 in bfloat16), up to 32 query heads, windows of 40 to 300 tokens, 6 to 30 experts
+    in up to 8 groups with up to 4 identity experts, four to seven layers."""
+    width = rng.choice([192, 256, 384, 512])
+
+    def mlp():
+        u = rng.random()
+        if u < 0.1:
+            return None
+        if u < 0.4:
+            return dense(rng.choice([320, 512, 200]), rng.choice([1.0, 2.0, 7.0]))
+        experts, identity = rng.choice([6, 12, 14, 30]), rng.choice([0, 2, 4, 2])
+        total = experts + identity
+        divisors = [g for g in (2, 4, 8) if total % g == 0]
+        groups = None
+        if divisors and rng.random() < 0.8:
+            g = rng.choice(divisors)
+            groups = (g, rng.randint(max(1, g // 2), g))
+        per_kept = total if groups is None else total // groups[0] * groups[1]
+        shared = None if rng.random() < 0.3 else (rng.choice([96, 64, 128]), rng.choice([1.0, 3.0]))
+        return moe(experts, rng.randint(1, min(6, per_kept)), rng.choice([96, 64, 80, 128]), identity, groups, rng.choice([1.0, 2.0, 2.5]),
+                   rng.choice([1.0, 4.0]), shared)
+
+    layers = []
+    for _ in range(rng.randint(4, 7)):
+        kind = rng.choice(["ret", "att", "at2", "at2"])
+        if kind == "ret":
+            heads, dim = rng.choice([2, 4, 6, 8]), rng.choice([32, 64, 96, 128])
+            rot = None if rng.random() < 0.2 else (rng.choice([1e4, 1e6]), rng.choice([d for d in (16, 32, dim) if d <= dim]))
+            layers.append(retention(heads, dim, rng.choice([32, 64, 128]), [1 - 2.0 ** -rng.randint(3, 11) for _ in range(heads)], rot, mlp()))
+        elif kind == "att":
+            kv = rng.choice([1, 2, 4]); heads = kv * rng.choice([1, 2, 4]); dim = rng.choice([32, 64, 96, 128])
+            sc = None if rng.random() < 0.3 else (rng.choice([4.0, 16.0]), rng.choice([256, 512, 4096]), rng.choice([16.0, 24.0]), rng.choice([1.0, 2.0]))
+            rot = None if rng.random() < 0.15 else (rng.choice([1e4, 5e5]), rng.choice([d for d in (16, 32, 64, dim) if d <= dim]), sc)
+            layers.append(attention(heads, kv, dim, rng.choice([32, 64, 128]), rng.choice([40, 72, 100, 128, 200, 300]), rng.uniform(0.05, 0.2), rot, mlp()))
+        else:
+            sources = [j for j, L in enumerate(layers) if L["type"] == "attention_2" and "kv_from" not in L["mixer"]]
+            temp = None if rng.random() < 0.2 else (rng.uniform(0.1, 0.4), rng.choice([32, 50, 128, 100]))
+            window = rng.choice([48, 64, 100, 130, 256])
+            if sources and rng.random() < 0.5:
+                j = rng.choice(sources)
+                src = layers[j]["mixer"]
+                layers.append(attention_2(src["heads"], src["kv_heads"], src["dim"], src["vdim"], window, rng.uniform(0.05, 0.2), temp, j, mlp()))
+            else:
+                kv = rng.choice([1, 2, 4]); heads = kv * rng.choice([1, 2, 4, 8])
+                layers.append(attention_2(heads, kv, rng.choice([32, 64, 96, 128]), rng.choice([32, 64, 128]), window, rng.uniform(0.05, 0.2), temp, None, mlp()))
+    cfg = {"architecture": "Koduzen", "vocab": rng.choice([300, 500, 1000]), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    streams = rng.choice([None, 1, 2, 2, 3, 4])
+    if streams is not None:
+        cfg["streams"] = streams
+    return cfg
+
+
 def config(name: str, **overrides) -> dict:
     c = copy.deepcopy(CONFIGS[name])
     c.update(overrides)

@@ -552,6 +552,31 @@ def test_configurations_drawn_at_random_under_every_kind_of_cut(seed, tmp_path):
             KH.compare(folder, requests, got, routing, dtype, stray=4 if dtype == "bfloat16" else 0)
 
 
+@pytest.mark.parametrize("seed", [1, 4, 9])
+def test_mid_size_configurations_on_pages_of_64_tokens(seed, tmp_path):
+    """Widths of 192 to 512, head sizes up to 128, dozens of experts, windows of up to 300 tokens, prompts of up to 700
+    tokens on pages of 64: whole prompts, a decoded tail, portions and mixed batches against the plain implementation.
+    Weights are drawn with a spread of 0.9 / sqrt(width) (what the tiny configurations have at their widths); the
+    float32 cap is 1e-4 here: rows are sums of up to 512 terms through up to seven layers."""
+    import jax_llm_examples_b200 as J
+
+    rng = random.Random(1000 + seed)
+    cfg = KH.mid_size_config(rng)
+    folder = J.write_random_model(tmp_path / "m", cfg, seed, norm_noise=0.1, std=0.9 / cfg["width"] ** 0.5)
+    requests = H.random_requests(rng, cfg["vocab"], [700, 330, 97, 23, 1, 260])
+    saved = dict(KH.TOL), dict(KH.TOL_MEAN)
+    KH.TOL["float32"], KH.TOL_MEAN["float32"] = 1e-4, 2e-5
+    try:
+        for dtype in ("float32", "bfloat16"):
+            engine = _engine(folder, dtype, max_tokens=1536, page_size=64, max_seq_len=1536)
+            for steps in (H.trace_whole(requests), H.trace_tail_decode(requests, tail=40), H.trace_portions(requests, rng),
+                          H.trace_mixed(requests, rng, max_live=4)):
+                got, routing = H.run_trace(engine, steps, record_routing=True)
+                KH.compare(folder, requests, got, routing, dtype, stray=6 if dtype == "bfloat16" else 0)
+    finally:
+        KH.TOL.update(saved[0]), KH.TOL_MEAN.update(saved[1])
+
+
 @pytest.mark.parametrize("name", list(KH.CONFIGS))
 def test_logits_do_not_depend_on_the_cut_or_on_the_batch(folders, name):
     """float32: the same request whole, token by token, in portions, and beside three other requests gives the same
